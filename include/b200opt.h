@@ -1,0 +1,271 @@
+/*
+ * b200opt — C ABI of the B200-native replacement for Saga's data-parallel
+ * parameter update: gradient reduce-scatter across GPUs, mixed-precision Adam
+ * with overflow detection and unscale on the locally owned shard, and the
+ * all-gather of the updated weights, run as ONE fused sm_100a kernel per rank
+ * that reads and writes peer GPU memory directly over NVLink.
+ *
+ * Everything here is plain C: opaque handles, raw device/host pointers, sizes
+ * and status codes.  No exception and no abort crosses this boundary.
+ *
+ * Paths in "replaces" notes are relative to the Saga project root.
+ *
+ * Threading: b200opt_step / b200opt_step_host / b200opt_flags may be called
+ * concurrently from different host threads as long as each thread uses a
+ * different handle (one handle == one rank == one GPU), which is how Saga
+ * drives its contexts (one std::thread per GPU, test/test_classifier.cpp:689).
+ * Creation, wiring and destruction are not thread-safe.
+ */
+#ifndef B200OPT_H
+#define B200OPT_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define B200OPT_API __attribute__((visibility("default")))
+#else
+#define B200OPT_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200OPT_MAX_RANKS 8
+
+/* status codes */
+#define B200OPT_OK 0
+#define B200OPT_EINVAL (-1)       /* bad argument */
+#define B200OPT_ECUDA (-2)        /* a CUDA runtime call failed; see b200opt_last_error */
+#define B200OPT_ENOMEM (-3)       /* device or host allocation failed */
+#define B200OPT_ETIMEOUT (-4)     /* a peer rank did not arrive within the wait limit */
+#define B200OPT_ESTATE (-5)       /* call not valid in the handle's state (peers not wired, ...) */
+#define B200OPT_EUNSUPPORTED (-6) /* built without the needed support (e.g. NCCL) */
+
+/* dtype groups, the two the reference builds optimizers for
+ * (src/cuda/cuda_optimizer.cpp:276-292) */
+#define B200OPT_HALF 0
+#define B200OPT_FLOAT 1
+
+/* loss-scale policies for b200opt_policy_update */
+#define B200OPT_POLICY_REFERENCE 0 /* src/cuda/cuda_program.cpp:295-302 */
+#define B200OPT_POLICY_INTERVAL 1  /* halve on inf/nan, double after N clean steps */
+
+/* collective paths for b200opt_set_option(B200OPT_OPT_PATH) */
+#define B200OPT_PATH_AUTO 0 /* peer kernel, NCCL below the measured crossover */
+#define B200OPT_PATH_PEER 1 /* fused peer-memory kernel always */
+#define B200OPT_PATH_NCCL 2 /* ncclReduceScatter + Adam kernel + ncclAllGather */
+
+/* options */
+#define B200OPT_OPT_TIMEOUT_MS 1    /* limit of every cross-GPU wait (default 10000) */
+#define B200OPT_OPT_PATH 2          /* B200OPT_PATH_* */
+#define B200OPT_OPT_CTAS_PER_SM 3   /* launch shape of the fused kernel (tuning) */
+#define B200OPT_OPT_KERNEL_VARIANT 4 /* 0 = direct 16-byte loads, 1 = bulk-copy staged (tuning) */
+#define B200OPT_OPT_NCCL_CROSSOVER 5 /* AUTO uses NCCL when n_half is below this many elements */
+
+typedef struct b200opt b200opt_t;
+
+/* ------------------------------------------------------------------ version */
+
+/* Returns a static string such as "b200opt 0.1 sm_100a". */
+B200OPT_API const char *b200opt_version(void);
+
+/* Human-readable text for a status code. */
+B200OPT_API const char *b200opt_strerror(int status);
+
+/* Text of the last failure recorded on this handle ("" if none). */
+B200OPT_API const char *b200opt_last_error(const b200opt_t *h);
+
+/* ----------------------------------------------------------------- creation */
+
+/*
+ * Creates rank `rank` of `nranks` on CUDA device `device`, owning
+ *   - the flat weight and gradient buffers of both dtype groups
+ *     (n_half fp16 elements and n_float fp32 elements each, zero-filled), and
+ *   - the shard-sized Adam state m, v (and the fp32 master copy for the fp16
+ *     group), zero-filled.
+ * Replaces the allocation half of CudaProgram::create_optimizer
+ * (src/cuda/cuda_optimizer.cpp:221-229: one [weights | gradients] allocation
+ * per dtype) and the AdamF32 / AdamMixed constructors (:64-74, :122-146).
+ * The shard of rank r is elements [r*(n/nranks), (r+1)*(n/nranks)) of each
+ * flat buffer, the reference's partition (:85-86, :157-158); elements beyond
+ * nranks*(n/nranks) are never updated, as in the reference.
+ * Either count may be 0.  nranks <= B200OPT_MAX_RANKS.
+ * With nranks > 1 the peers must be wired (below) before the first step.
+ */
+B200OPT_API int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
+                   size_t n_half, size_t n_float);
+
+/*
+ * Single-process convenience: creates all ranks and wires them to one another,
+ * the counterpart of CudaEngine::createContexts(multi=true) +
+ * ncclCommInitAll (src/cuda/cuda_common.cpp:89-129).  devices[i] is the CUDA
+ * device of rank i.  When several ranks name the SAME device the group runs in
+ * serial mode: kernels of different ranks never wait for one another (they
+ * could not run concurrently on one GPU); instead the caller must have written
+ * every rank's gradients before stepping any rank, must step every rank, and
+ * reads flags only after all ranks stepped.  Serial mode exists so that the
+ * multi-rank arithmetic can be checked on a single GPU.
+ */
+B200OPT_API int b200opt_create_group(b200opt_t **out, int nranks, const int *devices,
+                         size_t n_half, size_t n_float);
+
+/* Frees everything the handle owns.  Streams belong to the caller. */
+B200OPT_API int b200opt_destroy(b200opt_t *h);
+
+/* ------------------------------------------------------------- peer wiring */
+
+/*
+ * One rank per process (torchrun-style launch): every rank exports 64 bytes,
+ * the launcher exchanges them (any host transport), and every rank attaches
+ * every other rank's bytes.  Replaces the role of ncclCommInitAll
+ * (src/cuda/cuda_common.cpp:116-127).
+ */
+#define B200OPT_IPC_HANDLE_BYTES 64
+B200OPT_API int b200opt_ipc_export(b200opt_t *h, void *handle_out);
+B200OPT_API int b200opt_ipc_attach(b200opt_t *h, int peer_rank, const void *handle);
+
+/* Same process, other rank's handle (what b200opt_create_group does). */
+B200OPT_API int b200opt_attach_local(b200opt_t *h, int peer_rank, b200opt_t *peer);
+
+/*
+ * Optional NCCL communicator for the fallback path.  `unique_id` is the 128
+ * bytes of an ncclUniqueId that rank 0 obtained from
+ * b200opt_nccl_unique_id and the launcher distributed.
+ */
+#define B200OPT_NCCL_ID_BYTES 128
+B200OPT_API int b200opt_nccl_unique_id(void *unique_id_out);
+B200OPT_API int b200opt_nccl_init(b200opt_t *h, const void *unique_id);
+
+/* ------------------------------------------------------------------ buffers */
+
+/*
+ * Device pointers of this rank's flat weight and gradient buffers of one dtype
+ * group and their element count, so that the caller can point its tensors into
+ * them exactly as create_optimizer re-points Saga's tensor storages
+ * (src/cuda/cuda_optimizer.cpp:245-249).  Valid until b200opt_destroy.
+ */
+B200OPT_API int b200opt_buffers(b200opt_t *h, int dtype, void **weights, void **gradients,
+                    size_t *n);
+
+/*
+ * The reference's flat layout: tensor j starts at the sum of the sizes before
+ * it, each rounded up to a multiple of 16 elements
+ * (src/cuda/cuda_optimizer.cpp:199-219,235-258).  Writes k offsets (may be
+ * NULL) and returns the padded total through *total.  Host-only.
+ */
+B200OPT_API int b200opt_layout(const size_t *sizes, size_t k, size_t *offsets,
+                   size_t *total);
+
+/*
+ * After the initial weights have been written into the weight buffers:
+ * master := float(fp16 weight) over this rank's shard, m = v = 0, iteration
+ * counter = 0.  Replaces the host loop of the AdamMixed constructor
+ * (src/cuda/cuda_optimizer.cpp:142-145).  Asynchronous on `stream`.
+ */
+B200OPT_API int b200opt_init_master(b200opt_t *h, void *stream);
+
+/* --------------------------------------------------------------------- step */
+
+/*
+ * One optimizer step for both dtype groups of this rank, enqueued on `stream`
+ * (a cudaStream_t) and asynchronous: replaces AdamF32::exec + AdamMixed::exec
+ * (src/cuda/cuda_optimizer.cpp:76-113,148-186) and the 12-byte flag all-reduce
+ * of CudaProgram::step (src/cuda/cuda_program.cpp:282-291).
+ *   lr, l2_lambda  ProgramConfig::learning_rate / l2_lambda (saga.hpp:500-503)
+ *   scale          the program's current loss scale (m_mp_scaling); the fp16
+ *                  group's gradients are multiplied by 1.0f/scale
+ * The iteration counter advances on every call, overflow or not.
+ * All ranks must call it the same number of times; with nranks > 1 the kernel
+ * waits (bounded) for every peer's call of the same step.
+ */
+B200OPT_API int b200opt_step(b200opt_t *h, float lr, float l2_lambda, float scale,
+                 void *stream);
+
+/*
+ * Same step, gradients taken from HOST memory: copies grads_half (n_half fp16)
+ * and grads_float (n_float fp32) into the gradient buffers on `stream`, steps,
+ * waits for the stream and returns the flag sums.  Either pointer may be NULL
+ * when its group is empty.  Pinned host memory makes the copies asynchronous.
+ */
+B200OPT_API int b200opt_step_host(b200opt_t *h, const void *grads_half,
+                      const void *grads_float, float lr, float l2_lambda,
+                      float scale, void *stream, uint32_t flags_out[3]);
+
+/*
+ * Waits for `stream`, then returns the sums over ranks of {range, inf, nan}
+ * raised by the last step and clears them: the values CudaProgram::step reads
+ * from m_aux after its stream synchronise (src/cuda/cuda_program.cpp:293-306).
+ * Returns B200OPT_ETIMEOUT if a cross-GPU wait of that step ran out; the
+ * handle then refuses further steps.
+ */
+B200OPT_API int b200opt_flags(b200opt_t *h, void *stream, uint32_t flags_out[3]);
+
+/*
+ * The loss-scale update of CudaProgram::step (src/cuda/cuda_program.cpp:295-302),
+ * bit for bit: scale is a float, the factors are double.
+ *   B200OPT_POLICY_REFERENCE: inf or nan -> x0.5; else range > 1 -> x0.9; else x1.02
+ *   B200OPT_POLICY_INTERVAL:  inf or nan -> x0.5 and *state = 0; else
+ *                             ++*state == interval -> x2.0 and *state = 0
+ * `state` and `interval` are ignored by the reference policy.  Host-only.
+ */
+B200OPT_API int b200opt_policy_update(float *scale, const uint32_t flags[3], int policy,
+                          int *state, int interval);
+
+/* The two scalars AdamMixed::exec derives per step
+ * (src/cuda/cuda_optimizer.cpp:150-152): 1/(1-0.9^iter), 1/(1-0.999^iter),
+ * computed in double and narrowed to float.  Host-only. */
+B200OPT_API int b200opt_bias_corrections(int iter, float *b1t, float *b2t);
+
+/* ------------------------------------------------------------ kernel seam */
+
+/*
+ * Drop-in for saga::adam_mixed (src/cuda/cuda_kernels.hpp:61-64,
+ * src/cuda/cuda_kernels.cu:241-250) on caller-owned device memory, one GPU, no
+ * collective.  `aux` points at device-accessible {range, inf, nan, anomaly}
+ * words (src/cuda/cuda_aux.hpp:5-10); flags seen are stored as 1.
+ * Any pointer alignment is accepted; 16-byte aligned pointers take the
+ * vectorised path.
+ */
+B200OPT_API int b200opt_adam_mixed(size_t n, float alpha, void *weights,
+                       const void *gradients, float *mvec, float *vvec,
+                       float *cvec, float b1t, float b2t, float learning_rate,
+                       float l2_lambda, uint32_t *aux, void *stream);
+
+/* Drop-in for saga::adam_float (src/cuda/cuda_kernels.hpp:57-59,
+ * src/cuda/cuda_kernels.cu:232-239). */
+B200OPT_API int b200opt_adam_float(size_t n, float *weights, const float *gradients,
+                       float *mvec, float *vvec, float b1t, float b2t,
+                       float learning_rate, float l2_lambda, uint32_t *aux,
+                       void *stream);
+
+/* ------------------------------------------------------- state and options */
+
+/* Iteration counter (AdamMixed::m_iter, src/cuda/cuda_optimizer.cpp:41). */
+B200OPT_API int b200opt_get_iter(const b200opt_t *h, int *iter);
+B200OPT_API int b200opt_set_iter(b200opt_t *h, int iter);
+
+/*
+ * Copies this rank's shard state to / from host memory (synchronous):
+ * which = 0 m, 1 v, 2 master (fp16 group only).  count receives / gives the
+ * shard length n/nranks.  The reference never saves this state
+ * (src/graph.cpp:60-104 saves weights only); these make an exact resume
+ * possible.
+ */
+B200OPT_API int b200opt_export_state(b200opt_t *h, int dtype, int which, float *host_dst,
+                         size_t capacity, size_t *count);
+B200OPT_API int b200opt_import_state(b200opt_t *h, int dtype, int which,
+                         const float *host_src, size_t count);
+
+B200OPT_API int b200opt_set_option(b200opt_t *h, int option, long value);
+B200OPT_API int b200opt_get_option(const b200opt_t *h, int option, long *value);
+
+/* Kernel launches this handle has issued since creation (its own kernels and,
+ * on the NCCL path, the NCCL calls). */
+B200OPT_API int b200opt_launch_count(const b200opt_t *h, uint64_t *launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200OPT_H */

@@ -1,0 +1,835 @@
+// Host side of the b200opt C ABI (include/b200opt.h): handle management, peer
+// wiring, launch of the fused step kernel.  Host-only arithmetic (loss-scale
+// policy, bias corrections, flat layout) lives in host_logic.cpp.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "fused_step.cuh"
+#include "nccl_path.h"
+
+using namespace b200;
+
+namespace {
+
+constexpr size_t kCtrlBytes = 4096;
+static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block must fit its page");
+
+inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+}  // namespace
+
+struct b200opt {
+    int rank = 0, nranks = 1, device = 0;
+    size_t n_half = 0, n_float = 0;
+    // shard geometry
+    size_t sh = 0, oh = 0, Ah = 0, sf = 0, of = 0, Af = 0;
+    // peer-mapped arena: [Ctrl page | W half | G half | W float | G float]
+    char *arena = nullptr;
+    size_t arena_bytes = 0;
+    size_t off_wh = 0, off_gh = 0, off_wf = 0, off_gf = 0;
+    char *peer_arena[kMaxRanks] = {};
+    bool peer_is_ipc[kMaxRanks] = {};
+    int peers_attached = 0;
+    // local state
+    float *mh = nullptr, *vh = nullptr, *ch = nullptr, *mf = nullptr,
+          *vf = nullptr;
+    size_t state_h_elems = 0, state_f_elems = 0;
+    HostResult *host = nullptr;      // pinned + mapped
+    HostResult *host_dev = nullptr;  // device alias of `host`
+    int iter = 0;
+    uint32_t epoch = 0;
+    bool serial = false;  // peers share a device: no in-kernel waits
+    bool failed = false;
+    int num_sms = 0;
+    long timeout_ms = 10000;
+    long path = B200OPT_PATH_AUTO;
+    long ctas_per_sm = 0;  // 0 = built-in default
+    long variant = 0;
+    long nccl_crossover = 0;
+    uint64_t launches = 0;
+    NcclPath *nccl = nullptr;
+    std::string err;
+};
+
+namespace {
+
+int fail(b200opt *h, int code, const char *what, cudaError_t ce = cudaSuccess)
+{
+    if(h) {
+        char buf[512];
+        if(ce != cudaSuccess)
+            snprintf(buf, sizeof(buf), "%s: %s", what, cudaGetErrorString(ce));
+        else
+            snprintf(buf, sizeof(buf), "%s", what);
+        h->err = buf;
+    }
+    return code;
+}
+
+#define CK(h, call)                                     \
+    do {                                                \
+        cudaError_t ce_ = (call);                       \
+        if(ce_ != cudaSuccess)                          \
+            return fail((h), B200OPT_ECUDA, #call, ce_); \
+    } while(0)
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = true;
+    explicit DeviceGuard(int dev)
+    {
+        if(cudaGetDevice(&prev) != cudaSuccess)
+            prev = -1;
+        ok = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard()
+    {
+        if(prev >= 0)
+            cudaSetDevice(prev);
+    }
+};
+
+template <typename T>
+T *arena_ptr(char *base, size_t off)
+{
+    return base ? reinterpret_cast<T *>(base + off) : nullptr;
+}
+
+void fill_groups(const b200opt *h, StepParams &p)
+{
+    for(int q = 0; q < h->nranks; q++) {
+        char *base = h->peer_arena[q];
+        p.ctrl[q] = arena_ptr<Ctrl>(base, 0);
+        p.h.W[q] = arena_ptr<uint16_t>(base, h->off_wh);
+        p.h.G[q] = arena_ptr<uint16_t>(base, h->off_gh);
+        p.f.W[q] = arena_ptr<float>(base, h->off_wf);
+        p.f.G[q] = arena_ptr<float>(base, h->off_gf);
+    }
+    p.h.m = h->mh;
+    p.h.v = h->vh;
+    p.h.c = h->ch;
+    p.h.o = h->oh;
+    p.h.s = h->sh;
+    p.h.A = h->Ah;
+    p.h.ngroups = h->sh ? (h->oh + h->sh - h->Ah + kVec - 1) / kVec : 0;
+    p.f.m = h->mf;
+    p.f.v = h->vf;
+    p.f.o = h->of;
+    p.f.s = h->sf;
+    p.f.A = h->Af;
+    p.f.ngroups = h->sf ? (h->of + h->sf - h->Af + kVec - 1) / kVec : 0;
+}
+
+template <int NR, int UNR, int MINB>
+cudaError_t launch_variant(const StepParams &p, int grid, cudaStream_t st)
+{
+    fused_step_kernel<NR, UNR, MINB><<<grid, kThreads, 0, st>>>(p);
+    return cudaGetLastError();
+}
+
+// Launch shape: a persistent grid of ctas_per_sm CTAs on every SM, shrunk for
+// small inputs so that no CTA starts without work.
+//   variant 0: one 8-element group per thread per trip
+//   variant 1: two groups per thread per trip (one rank only)
+cudaError_t launch_step(const StepParams &p, int nranks, int num_sms,
+                        long ctas_per_sm, long variant, cudaStream_t st)
+{
+    const size_t groups = std::max(p.h.ngroups, p.f.ngroups);
+    const int unr = (nranks == 1 && variant == 1) ? 2 : 1;
+    const long def_ctas = nranks == 1 ? (variant == 1 ? 2 : 3) : 2;
+    const long cps = ctas_per_sm > 0 ? ctas_per_sm : def_ctas;
+    size_t want = (groups + (size_t)kThreads * unr - 1) / ((size_t)kThreads * unr);
+    if(want == 0)
+        want = 1;
+    const int grid = (int)std::min<size_t>(want, (size_t)num_sms * cps);
+    switch(nranks) {
+    case 1:
+        return variant == 1 ? launch_variant<1, 2, 2>(p, grid, st)
+                            : launch_variant<1, 1, 3>(p, grid, st);
+    case 2: return launch_variant<2, 1, 3>(p, grid, st);
+    case 3: return launch_variant<3, 1, 2>(p, grid, st);
+    case 4: return launch_variant<4, 1, 2>(p, grid, st);
+    case 5: return launch_variant<5, 1, 2>(p, grid, st);
+    case 6: return launch_variant<6, 1, 2>(p, grid, st);
+    case 7: return launch_variant<7, 1, 2>(p, grid, st);
+    case 8: return launch_variant<8, 1, 2>(p, grid, st);
+    }
+    return cudaErrorInvalidValue;
+}
+
+bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+const char *b200opt_version(void) { return "b200opt 0.1 sm_100a"; }
+
+const char *b200opt_strerror(int status)
+{
+    switch(status) {
+    case B200OPT_OK: return "ok";
+    case B200OPT_EINVAL: return "invalid argument";
+    case B200OPT_ECUDA: return "CUDA runtime error";
+    case B200OPT_ENOMEM: return "out of memory";
+    case B200OPT_ETIMEOUT: return "a peer rank did not arrive in time";
+    case B200OPT_ESTATE: return "call not valid in this state";
+    case B200OPT_EUNSUPPORTED: return "not supported by this build";
+    }
+    return "unknown status";
+}
+
+const char *b200opt_last_error(const b200opt_t *h)
+{
+    return h ? h->err.c_str() : "";
+}
+
+int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
+                   size_t n_half, size_t n_float)
+{
+    if(!out || nranks < 1 || nranks > kMaxRanks || rank < 0 || rank >= nranks ||
+       device < 0)
+        return B200OPT_EINVAL;
+    *out = nullptr;
+    int ndev = 0;
+    if(cudaGetDeviceCount(&ndev) != cudaSuccess || device >= ndev)
+        return B200OPT_ECUDA;
+
+    b200opt *h = new(std::nothrow) b200opt;
+    if(!h)
+        return B200OPT_ENOMEM;
+    h->rank = rank;
+    h->nranks = nranks;
+    h->device = device;
+    h->n_half = n_half;
+    h->n_float = n_float;
+    // the reference's partition: plain integer division
+    // (src/cuda/cuda_optimizer.cpp:85-86,157-158 of the Saga tree)
+    h->sh = n_half / nranks;
+    h->oh = h->sh * rank;
+    h->Ah = h->oh & ~(size_t)(kVec - 1);
+    h->sf = n_float / nranks;
+    h->of = h->sf * rank;
+    h->Af = h->of & ~(size_t)(kVec - 1);
+
+    h->off_wh = kCtrlBytes;
+    h->off_gh = h->off_wh + round_up(n_half * 2, 256);
+    h->off_wf = h->off_gh + round_up(n_half * 2, 256);
+    h->off_gf = h->off_wf + round_up(n_float * 4, 256);
+    h->arena_bytes = h->off_gf + round_up(n_float * 4, 256);
+
+    DeviceGuard guard(device);
+    int rc = B200OPT_OK;
+    cudaError_t ce = cudaSuccess;
+    do {
+        if(!guard.ok) {
+            rc = B200OPT_ECUDA;
+            break;
+        }
+        cudaDeviceProp prop;
+        if((ce = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) {
+            rc = B200OPT_ECUDA;
+            break;
+        }
+        h->num_sms = prop.multiProcessorCount;
+        if((ce = cudaMalloc(&h->arena, h->arena_bytes)) != cudaSuccess) {
+            rc = B200OPT_ENOMEM;
+            break;
+        }
+        if((ce = cudaMemset(h->arena, 0, h->arena_bytes)) != cudaSuccess) {
+            rc = B200OPT_ECUDA;
+            break;
+        }
+        // shard state, padded so that element i of the flat buffer sits at
+        // [i - A]: the vector path then sees the same 8-element phase in every
+        // array
+        h->state_h_elems = h->sh ? round_up(h->oh + h->sh - h->Ah, kVec) : 0;
+        h->state_f_elems = h->sf ? round_up(h->of + h->sf - h->Af, kVec) : 0;
+        float **hs[3] = {&h->mh, &h->vh, &h->ch};
+        for(auto pp : hs) {
+            if(!h->state_h_elems)
+                continue;
+            if((ce = cudaMalloc(pp, h->state_h_elems * 4)) != cudaSuccess) {
+                rc = B200OPT_ENOMEM;
+                break;
+            }
+            cudaMemset(*pp, 0, h->state_h_elems * 4);
+        }
+        if(rc)
+            break;
+        float **fs[2] = {&h->mf, &h->vf};
+        for(auto pp : fs) {
+            if(!h->state_f_elems)
+                continue;
+            if((ce = cudaMalloc(pp, h->state_f_elems * 4)) != cudaSuccess) {
+                rc = B200OPT_ENOMEM;
+                break;
+            }
+            cudaMemset(*pp, 0, h->state_f_elems * 4);
+        }
+        if(rc)
+            break;
+        if((ce = cudaHostAlloc(&h->host, sizeof(HostResult),
+                               cudaHostAllocMapped | cudaHostAllocPortable)) !=
+           cudaSuccess) {
+            rc = B200OPT_ENOMEM;
+            break;
+        }
+        memset(h->host, 0, sizeof(HostResult));
+        if((ce = cudaHostGetDevicePointer((void **)&h->host_dev, h->host, 0)) !=
+           cudaSuccess) {
+            rc = B200OPT_ECUDA;
+            break;
+        }
+        if((ce = cudaDeviceSynchronize()) != cudaSuccess) {
+            rc = B200OPT_ECUDA;
+            break;
+        }
+    } while(0);
+    if(rc) {
+        (void)ce;
+        b200opt_destroy(h);
+        return rc;
+    }
+    h->peer_arena[rank] = h->arena;
+    h->peers_attached = 1;
+    *out = h;
+    return B200OPT_OK;
+}
+
+int b200opt_destroy(b200opt_t *h)
+{
+    if(!h)
+        return B200OPT_EINVAL;
+    DeviceGuard guard(h->device);
+    cudaDeviceSynchronize();
+    if(h->nccl)
+        nccl_path_destroy(h->nccl);
+    for(int q = 0; q < h->nranks; q++) {
+        if(q != h->rank && h->peer_arena[q] && h->peer_is_ipc[q])
+            cudaIpcCloseMemHandle(h->peer_arena[q]);
+    }
+    cudaFree(h->arena);
+    cudaFree(h->mh);
+    cudaFree(h->vh);
+    cudaFree(h->ch);
+    cudaFree(h->mf);
+    cudaFree(h->vf);
+    if(h->host)
+        cudaFreeHost(h->host);
+    delete h;
+    return B200OPT_OK;
+}
+
+int b200opt_attach_local(b200opt_t *h, int peer_rank, b200opt_t *peer)
+{
+    if(!h || !peer || peer_rank < 0 || peer_rank >= h->nranks ||
+       peer_rank == h->rank || peer->rank != peer_rank ||
+       peer->nranks != h->nranks)
+        return B200OPT_EINVAL;
+    if(peer->n_half != h->n_half || peer->n_float != h->n_float)
+        return fail(h, B200OPT_EINVAL, "peer was created with other sizes");
+    if(h->peer_arena[peer_rank])
+        return fail(h, B200OPT_ESTATE, "peer already attached");
+    if(peer->device == h->device) {
+        h->serial = true;
+    } else {
+        DeviceGuard guard(h->device);
+        int can = 0;
+        CK(h, cudaDeviceCanAccessPeer(&can, h->device, peer->device));
+        if(!can)
+            return fail(h, B200OPT_EUNSUPPORTED,
+                        "no peer access between the two devices");
+        cudaError_t ce = cudaDeviceEnablePeerAccess(peer->device, 0);
+        if(ce == cudaErrorPeerAccessAlreadyEnabled)
+            cudaGetLastError();
+        else if(ce != cudaSuccess)
+            return fail(h, B200OPT_ECUDA, "cudaDeviceEnablePeerAccess", ce);
+    }
+    h->peer_arena[peer_rank] = peer->arena;
+    h->peers_attached++;
+    return B200OPT_OK;
+}
+
+int b200opt_create_group(b200opt_t **out, int nranks, const int *devices,
+                         size_t n_half, size_t n_float)
+{
+    if(!out || !devices || nranks < 1 || nranks > kMaxRanks)
+        return B200OPT_EINVAL;
+    for(int r = 0; r < nranks; r++)
+        out[r] = nullptr;
+    int rc = B200OPT_OK;
+    for(int r = 0; r < nranks && !rc; r++)
+        rc = b200opt_create(&out[r], r, nranks, devices[r], n_half, n_float);
+    bool any_shared = false;
+    for(int r = 0; r < nranks; r++)
+        for(int q = 0; q < r; q++)
+            any_shared |= devices[r] == devices[q];
+    for(int r = 0; r < nranks && !rc; r++)
+        for(int q = 0; q < nranks && !rc; q++)
+            if(q != r)
+                rc = b200opt_attach_local(out[r], q, out[q]);
+    if(!rc && any_shared)
+        for(int r = 0; r < nranks; r++)
+            out[r]->serial = true;
+    if(rc) {
+        for(int r = 0; r < nranks; r++) {
+            if(out[r])
+                b200opt_destroy(out[r]);
+            out[r] = nullptr;
+        }
+    }
+    return rc;
+}
+
+int b200opt_ipc_export(b200opt_t *h, void *handle_out)
+{
+    if(!h || !handle_out)
+        return B200OPT_EINVAL;
+    static_assert(sizeof(cudaIpcMemHandle_t) == B200OPT_IPC_HANDLE_BYTES,
+                  "IPC handle size");
+    DeviceGuard guard(h->device);
+    cudaIpcMemHandle_t mh;
+    CK(h, cudaIpcGetMemHandle(&mh, h->arena));
+    memcpy(handle_out, &mh, sizeof(mh));
+    return B200OPT_OK;
+}
+
+int b200opt_ipc_attach(b200opt_t *h, int peer_rank, const void *handle)
+{
+    if(!h || !handle || peer_rank < 0 || peer_rank >= h->nranks ||
+       peer_rank == h->rank)
+        return B200OPT_EINVAL;
+    if(h->peer_arena[peer_rank])
+        return fail(h, B200OPT_ESTATE, "peer already attached");
+    DeviceGuard guard(h->device);
+    cudaIpcMemHandle_t mh;
+    memcpy(&mh, handle, sizeof(mh));
+    void *p = nullptr;
+    CK(h, cudaIpcOpenMemHandle(&p, mh, cudaIpcMemLazyEnablePeerAccess));
+    h->peer_arena[peer_rank] = (char *)p;
+    h->peer_is_ipc[peer_rank] = true;
+    h->peers_attached++;
+    return B200OPT_OK;
+}
+
+int b200opt_nccl_unique_id(void *unique_id_out)
+{
+    if(!unique_id_out)
+        return B200OPT_EINVAL;
+    return nccl_path_unique_id(unique_id_out);
+}
+
+int b200opt_nccl_init(b200opt_t *h, const void *unique_id)
+{
+    if(!h || !unique_id)
+        return B200OPT_EINVAL;
+    if(h->nccl)
+        return fail(h, B200OPT_ESTATE, "NCCL communicator already created");
+    DeviceGuard guard(h->device);
+    std::string err;
+    int rc = nccl_path_create(&h->nccl, h->rank, h->nranks, unique_id, &err);
+    if(rc)
+        return fail(h, rc, err.c_str());
+    return B200OPT_OK;
+}
+
+int b200opt_buffers(b200opt_t *h, int dtype, void **weights, void **gradients,
+                    size_t *n)
+{
+    if(!h || (dtype != B200OPT_HALF && dtype != B200OPT_FLOAT))
+        return B200OPT_EINVAL;
+    const bool half = dtype == B200OPT_HALF;
+    if(weights)
+        *weights = h->arena + (half ? h->off_wh : h->off_wf);
+    if(gradients)
+        *gradients = h->arena + (half ? h->off_gh : h->off_gf);
+    if(n)
+        *n = half ? h->n_half : h->n_float;
+    return B200OPT_OK;
+}
+
+int b200opt_init_master(b200opt_t *h, void *stream)
+{
+    if(!h)
+        return B200OPT_EINVAL;
+    DeviceGuard guard(h->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    if(h->state_h_elems) {
+        CK(h, cudaMemsetAsync(h->mh, 0, h->state_h_elems * 4, st));
+        CK(h, cudaMemsetAsync(h->vh, 0, h->state_h_elems * 4, st));
+        CK(h, cudaMemsetAsync(h->ch, 0, h->state_h_elems * 4, st));
+        const int grid = (int)std::min<size_t>((h->sh + 255) / 256,
+                                               (size_t)h->num_sms * 8);
+        init_master_kernel<<<grid, 256, 0, st>>>(
+            arena_ptr<uint16_t>(h->arena, h->off_wh), h->ch, h->oh, h->sh,
+            h->Ah);
+        CK(h, cudaGetLastError());
+        h->launches++;
+    }
+    if(h->state_f_elems) {
+        CK(h, cudaMemsetAsync(h->mf, 0, h->state_f_elems * 4, st));
+        CK(h, cudaMemsetAsync(h->vf, 0, h->state_f_elems * 4, st));
+    }
+    h->iter = 0;
+    return B200OPT_OK;
+}
+
+int b200opt_step(b200opt_t *h, float lr, float l2_lambda, float scale,
+                 void *stream)
+{
+    if(!h)
+        return B200OPT_EINVAL;
+    if(h->failed)
+        return fail(h, B200OPT_ESTATE,
+                    "an earlier step timed out; the handle is unusable");
+    if(h->peers_attached != h->nranks)
+        return fail(h, B200OPT_ESTATE, "not every peer rank is attached");
+    DeviceGuard guard(h->device);
+    cudaStream_t st = (cudaStream_t)stream;
+
+    // src/cuda/cuda_optimizer.cpp:150-152,169 of the Saga tree
+    const int iter = ++h->iter;
+    StepParams p;
+    memset(&p, 0, sizeof(p));
+    b200opt_bias_corrections(iter, &p.b1t, &p.b2t);
+    p.alpha = 1.0f / scale;
+    p.lr = lr;
+    p.l2 = l2_lambda;
+    p.rank = h->rank;
+    p.epoch = ++h->epoch;
+    p.timeout_ns = (unsigned long long)h->timeout_ms * 1000000ull;
+    p.host = h->host_dev;
+
+    const bool use_nccl =
+        h->nranks > 1 && !h->serial &&
+        (h->path == B200OPT_PATH_NCCL ||
+         (h->path == B200OPT_PATH_AUTO && h->nccl &&
+          (long)h->n_half < h->nccl_crossover));
+    if(use_nccl) {
+        if(!h->nccl)
+            return fail(h, B200OPT_ESTATE,
+                        "NCCL path selected but b200opt_nccl_init was not called");
+        // reduce-scatter in place, Adam on the local shard, all-gather, flag sum
+        std::string err;
+        uint16_t *wh = arena_ptr<uint16_t>(h->arena, h->off_wh);
+        uint16_t *gh = arena_ptr<uint16_t>(h->arena, h->off_gh);
+        float *wf = arena_ptr<float>(h->arena, h->off_wf);
+        float *gf = arena_ptr<float>(h->arena, h->off_gf);
+        Ctrl *ctrl = arena_ptr<Ctrl>(h->arena, 0);
+        int rc = nccl_path_reduce_scatter(h->nccl, gh, h->sh, gf, h->sf, st,
+                                          &err);
+        if(rc)
+            return fail(h, rc, err.c_str());
+        // one-rank view of this rank's own memory: the shard now holds the sum
+        fill_groups(h, p);
+        for(int q = 0; q < kMaxRanks; q++) {
+            p.ctrl[q] = nullptr;
+            p.h.W[q] = nullptr;
+            p.h.G[q] = nullptr;
+            p.f.W[q] = nullptr;
+            p.f.G[q] = nullptr;
+        }
+        p.rank = 0;
+        p.ctrl[0] = ctrl;
+        p.h.W[0] = wh;
+        p.h.G[0] = gh;
+        p.f.W[0] = wf;
+        p.f.G[0] = gf;
+        p.host = nullptr;
+        p.flags_dev = ctrl->coll_flags;
+        p.barrier = 0;
+        CK(h, launch_step(p, 1, h->num_sms, h->ctas_per_sm, h->variant, st));
+        rc = nccl_path_all_gather_and_flags(h->nccl, wh, h->sh, wf, h->sf,
+                                            ctrl->coll_flags, st, &err);
+        if(rc)
+            return fail(h, rc, err.c_str());
+        CK(h, cudaMemcpyAsync(&h->host->range, ctrl->coll_flags, 12,
+                              cudaMemcpyDeviceToHost, st));
+        h->launches += 6;
+        return B200OPT_OK;
+    }
+
+    fill_groups(h, p);
+    p.barrier = (h->nranks > 1 && !h->serial) ? 1 : 0;
+    CK(h, launch_step(p, h->nranks, h->num_sms, h->ctas_per_sm, h->variant, st));
+    h->launches++;
+    return B200OPT_OK;
+}
+
+int b200opt_flags(b200opt_t *h, void *stream, uint32_t flags_out[3])
+{
+    if(!h || !flags_out)
+        return B200OPT_EINVAL;
+    DeviceGuard guard(h->device);
+    CK(h, cudaStreamSynchronize((cudaStream_t)stream));
+    if(h->host->status) {
+        h->failed = true;
+        char buf[160];
+        snprintf(buf, sizeof(buf),
+                 "step %u: rank %d gave up waiting for rank %u (%s)",
+                 h->epoch, h->rank, h->host->peer,
+                 h->host->where == 1 ? "gradients not announced"
+                                     : "completion not announced");
+        return fail(h, B200OPT_ETIMEOUT, buf);
+    }
+    if(h->serial && h->nranks > 1) {
+        // every rank's launch left its flag word in this rank's slot array
+        uint32_t words[32];
+        const Ctrl *c = arena_ptr<Ctrl>(h->arena, 0);
+        CK(h, cudaMemcpy(words, c->flagword[h->epoch & 1], sizeof(words),
+                         cudaMemcpyDeviceToHost));
+        flags_out[0] = flags_out[1] = flags_out[2] = 0;
+        for(int q = 0; q < h->nranks; q++) {
+            if(!(words[q] & kFlagValid))
+                return fail(h, B200OPT_ESTATE,
+                            "serial mode: not every rank has stepped yet");
+            flags_out[0] += (words[q] & kFlagRange) ? 1 : 0;
+            flags_out[1] += (words[q] & kFlagInf) ? 1 : 0;
+            flags_out[2] += (words[q] & kFlagNan) ? 1 : 0;
+        }
+        CK(h, cudaMemset((void *)c->flagword[h->epoch & 1], 0, sizeof(words)));
+    } else {
+        flags_out[0] = h->host->range;
+        flags_out[1] = h->host->inf;
+        flags_out[2] = h->host->nan;
+    }
+    h->host->range = h->host->inf = h->host->nan = 0;
+    return B200OPT_OK;
+}
+
+int b200opt_step_host(b200opt_t *h, const void *grads_half,
+                      const void *grads_float, float lr, float l2_lambda,
+                      float scale, void *stream, uint32_t flags_out[3])
+{
+    if(!h || !flags_out)
+        return B200OPT_EINVAL;
+    if((h->n_half && !grads_half) || (h->n_float && !grads_float))
+        return B200OPT_EINVAL;
+    DeviceGuard guard(h->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    if(h->n_half)
+        CK(h, cudaMemcpyAsync(h->arena + h->off_gh, grads_half, h->n_half * 2,
+                              cudaMemcpyHostToDevice, st));
+    if(h->n_float)
+        CK(h, cudaMemcpyAsync(h->arena + h->off_gf, grads_float,
+                              h->n_float * 4, cudaMemcpyHostToDevice, st));
+    int rc = b200opt_step(h, lr, l2_lambda, scale, stream);
+    if(rc)
+        return rc;
+    return b200opt_flags(h, stream, flags_out);
+}
+
+int b200opt_adam_mixed(size_t n, float alpha, void *weights,
+                       const void *gradients, float *mvec, float *vvec,
+                       float *cvec, float b1t, float b2t, float learning_rate,
+                       float l2_lambda, uint32_t *aux, void *stream)
+{
+    if(n && (!weights || !gradients || !mvec || !vvec || !cvec || !aux))
+        return B200OPT_EINVAL;
+    if(!n)
+        return B200OPT_OK;
+    int dev = 0, sms = 0;
+    if(cudaGetDevice(&dev) != cudaSuccess ||
+       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) !=
+           cudaSuccess)
+        return B200OPT_ECUDA;
+    StepParams p;
+    memset(&p, 0, sizeof(p));
+    p.h.W[0] = (uint16_t *)weights;
+    p.h.G[0] = (const uint16_t *)gradients;
+    p.h.m = mvec;
+    p.h.v = vvec;
+    p.h.c = cvec;
+    p.h.s = n;
+    p.h.ngroups = (n + kVec - 1) / kVec;
+    p.alpha = alpha;
+    p.b1t = b1t;
+    p.b2t = b2t;
+    p.lr = learning_rate;
+    p.l2 = l2_lambda;
+    p.aux = aux;
+    p.force_scalar = !(aligned16(weights) && aligned16(gradients) &&
+                       aligned16(mvec) && aligned16(vvec) && aligned16(cvec));
+    return launch_step(p, 1, sms, 0, 0, (cudaStream_t)stream) == cudaSuccess
+               ? B200OPT_OK
+               : B200OPT_ECUDA;
+}
+
+int b200opt_adam_float(size_t n, float *weights, const float *gradients,
+                       float *mvec, float *vvec, float b1t, float b2t,
+                       float learning_rate, float l2_lambda, uint32_t *aux,
+                       void *stream)
+{
+    if(n && (!weights || !gradients || !mvec || !vvec || !aux))
+        return B200OPT_EINVAL;
+    if(!n)
+        return B200OPT_OK;
+    int dev = 0, sms = 0;
+    if(cudaGetDevice(&dev) != cudaSuccess ||
+       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) !=
+           cudaSuccess)
+        return B200OPT_ECUDA;
+    StepParams p;
+    memset(&p, 0, sizeof(p));
+    p.f.W[0] = weights;
+    p.f.G[0] = gradients;
+    p.f.m = mvec;
+    p.f.v = vvec;
+    p.f.s = n;
+    p.f.ngroups = (n + kVec - 1) / kVec;
+    p.b1t = b1t;
+    p.b2t = b2t;
+    p.lr = learning_rate;
+    p.l2 = l2_lambda;
+    p.aux = aux;
+    p.force_scalar = !(aligned16(weights) && aligned16(gradients) &&
+                       aligned16(mvec) && aligned16(vvec));
+    return launch_step(p, 1, sms, 0, 0, (cudaStream_t)stream) == cudaSuccess
+               ? B200OPT_OK
+               : B200OPT_ECUDA;
+}
+
+int b200opt_get_iter(const b200opt_t *h, int *iter)
+{
+    if(!h || !iter)
+        return B200OPT_EINVAL;
+    *iter = h->iter;
+    return B200OPT_OK;
+}
+
+int b200opt_set_iter(b200opt_t *h, int iter)
+{
+    if(!h || iter < 0)
+        return B200OPT_EINVAL;
+    h->iter = iter;
+    return B200OPT_OK;
+}
+
+static int state_array(b200opt_t *h, int dtype, int which, float **base,
+                       size_t *skip, size_t *count)
+{
+    if(dtype == B200OPT_HALF) {
+        float *a[3] = {h->mh, h->vh, h->ch};
+        if(which < 0 || which > 2)
+            return B200OPT_EINVAL;
+        *base = a[which];
+        *skip = h->oh - h->Ah;
+        *count = h->sh;
+    } else if(dtype == B200OPT_FLOAT) {
+        float *a[2] = {h->mf, h->vf};
+        if(which < 0 || which > 1)
+            return B200OPT_EINVAL;
+        *base = a[which];
+        *skip = h->of - h->Af;
+        *count = h->sf;
+    } else {
+        return B200OPT_EINVAL;
+    }
+    return B200OPT_OK;
+}
+
+int b200opt_export_state(b200opt_t *h, int dtype, int which, float *host_dst,
+                         size_t capacity, size_t *count)
+{
+    if(!h)
+        return B200OPT_EINVAL;
+    float *base;
+    size_t skip, cnt;
+    int rc = state_array(h, dtype, which, &base, &skip, &cnt);
+    if(rc)
+        return rc;
+    if(count)
+        *count = cnt;
+    if(!host_dst)
+        return B200OPT_OK;
+    if(capacity < cnt)
+        return B200OPT_EINVAL;
+    DeviceGuard guard(h->device);
+    if(cnt)
+        CK(h, cudaMemcpy(host_dst, base + skip, cnt * 4,
+                         cudaMemcpyDeviceToHost));
+    return B200OPT_OK;
+}
+
+int b200opt_import_state(b200opt_t *h, int dtype, int which,
+                         const float *host_src, size_t count)
+{
+    if(!h || !host_src)
+        return B200OPT_EINVAL;
+    float *base;
+    size_t skip, cnt;
+    int rc = state_array(h, dtype, which, &base, &skip, &cnt);
+    if(rc)
+        return rc;
+    if(count != cnt)
+        return B200OPT_EINVAL;
+    DeviceGuard guard(h->device);
+    if(cnt)
+        CK(h, cudaMemcpy(base + skip, host_src, cnt * 4,
+                         cudaMemcpyHostToDevice));
+    return B200OPT_OK;
+}
+
+int b200opt_set_option(b200opt_t *h, int option, long value)
+{
+    if(!h)
+        return B200OPT_EINVAL;
+    switch(option) {
+    case B200OPT_OPT_TIMEOUT_MS:
+        if(value < 1)
+            return B200OPT_EINVAL;
+        h->timeout_ms = value;
+        return B200OPT_OK;
+    case B200OPT_OPT_PATH:
+        if(value < B200OPT_PATH_AUTO || value > B200OPT_PATH_NCCL)
+            return B200OPT_EINVAL;
+        h->path = value;
+        return B200OPT_OK;
+    case B200OPT_OPT_CTAS_PER_SM:
+        if(value < 0 || value > 32)
+            return B200OPT_EINVAL;
+        h->ctas_per_sm = value;
+        return B200OPT_OK;
+    case B200OPT_OPT_KERNEL_VARIANT:
+        if(value < 0 || value > 1)
+            return B200OPT_EINVAL;
+        h->variant = value;
+        return B200OPT_OK;
+    case B200OPT_OPT_NCCL_CROSSOVER:
+        if(value < 0)
+            return B200OPT_EINVAL;
+        h->nccl_crossover = value;
+        return B200OPT_OK;
+    }
+    return B200OPT_EINVAL;
+}
+
+int b200opt_get_option(const b200opt_t *h, int option, long *value)
+{
+    if(!h || !value)
+        return B200OPT_EINVAL;
+    switch(option) {
+    case B200OPT_OPT_TIMEOUT_MS: *value = h->timeout_ms; return B200OPT_OK;
+    case B200OPT_OPT_PATH: *value = h->path; return B200OPT_OK;
+    case B200OPT_OPT_CTAS_PER_SM: *value = h->ctas_per_sm; return B200OPT_OK;
+    case B200OPT_OPT_KERNEL_VARIANT: *value = h->variant; return B200OPT_OK;
+    case B200OPT_OPT_NCCL_CROSSOVER: *value = h->nccl_crossover; return B200OPT_OK;
+    }
+    return B200OPT_EINVAL;
+}
+
+int b200opt_launch_count(const b200opt_t *h, uint64_t *launches)
+{
+    if(!h || !launches)
+        return B200OPT_EINVAL;
+    *launches = h->launches;
+    return B200OPT_OK;
+}
+
+}  // extern "C"

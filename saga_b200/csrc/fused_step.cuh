@@ -1,0 +1,660 @@
+// Fused reduce-scatter + mixed-precision Adam + all-gather step kernel for
+// sm_100a, and the small helper kernels around it.
+//
+// What one launch does on rank r of N (one launch per rank per training step):
+//   1. (N > 1) tells every peer "my gradients are final" and waits, bounded,
+//      until every peer said the same;
+//   2. for its shard of each dtype group: loads the gradient vectors of all N
+//      ranks through peer-mapped pointers (16 bytes per thread per rank), sums
+//      them in fp32 in rank order, rounds once to the buffer dtype, classifies
+//      overflow on the rounded value, unscales, applies Adam to the local fp32
+//      m / v / master shard, and stores the new fp16 (or fp32) weights into the
+//      weight buffer of EVERY rank;
+//   3. the last CTA to finish publishes this rank's flag word to all peers,
+//      waits (bounded) for theirs, and writes the sums to pinned host memory.
+//
+// The arithmetic per element follows Saga's adam_kernel_mp / adam_kernel
+// (src/cuda/cuda_kernels.cu:159-230 of the Saga tree) expression by expression
+// so that nvcc contracts the same multiply-add pairs.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/b200opt.h"
+
+namespace b200 {
+
+constexpr int kThreads = 256;
+constexpr int kMaxRanks = B200OPT_MAX_RANKS;
+constexpr int kVec = 8;  // elements per thread per group (16 B of fp16)
+
+// flag bits carried in registers / flag words
+constexpr uint32_t kFlagRange = 1u;
+constexpr uint32_t kFlagInf = 2u;
+constexpr uint32_t kFlagNan = 4u;
+constexpr uint32_t kFlagValid = 0x80000000u;
+
+// Adam constants of the reference (src/cuda/cuda_kernels.hpp:54-55,
+// src/cuda/cuda_kernels.cu:157): double literals narrowed to float.
+#define B200OPT_ADAM_B1 0.9
+#define B200OPT_ADAM_B2 0.999
+#define B200OPT_ADAM_EPS 1e-8
+
+// Per-rank control block at the start of the peer-mapped arena.  Peers write
+// ready[], done[] and flagword[][]; the rest is touched by the owner only.
+struct alignas(128) Ctrl {
+    uint32_t ready[32];        // ready[q] = step number rank q has reached
+    uint32_t done[32];         // done[q]  = step number rank q has finished
+    uint32_t flagword[2][32];  // [step parity][q] flag bits of rank q | valid
+    uint32_t cta_done;         // CTAs of the running launch that finished
+    uint32_t local_flags;      // OR of this rank's flag bits
+    uint32_t status;           // sticky B200OPT_E* (as positive number) or 0
+    uint32_t pad0;
+    uint32_t coll_flags[4];    // NCCL path: {range, inf, nan} to be all-reduced
+    uint32_t pad[24];
+};
+
+// Written by the last CTA of a launch, read by the host after a stream sync.
+struct HostResult {
+    uint32_t range, inf, nan;
+    uint32_t status;  // 0 or -B200OPT_ETIMEOUT
+    uint32_t epoch;
+    uint32_t where;   // 1 = wait for gradients, 2 = wait for completion
+    uint32_t peer;    // rank that did not arrive
+    uint32_t pad;
+};
+
+struct HalfGroup {
+    uint16_t *W[kMaxRanks];        // weight buffer of every rank
+    const uint16_t *G[kMaxRanks];  // gradient buffer of every rank
+    float *m, *v, *c;  // local shard state; element i (global index) at [i - A]
+    size_t o, s;       // shard start and length, elements
+    size_t A;          // o rounded down to a multiple of kVec
+    size_t ngroups;    // kVec-element groups covering [A, o+s)
+};
+
+struct FloatGroup {
+    float *W[kMaxRanks];
+    const float *G[kMaxRanks];
+    float *m, *v;
+    size_t o, s, A, ngroups;
+};
+
+struct StepParams {
+    HalfGroup h;
+    FloatGroup f;
+    float alpha, b1t, b2t, lr, l2;
+    int rank;
+    int barrier;      // 1: wait for peers inside the kernel
+    int force_scalar; // 1: pointers are not 16-byte aligned, element-wise path
+    uint32_t epoch;
+    unsigned long long timeout_ns;
+    Ctrl *ctrl[kMaxRanks];  // control block of every rank (ctrl[rank] local)
+    HostResult *host;       // pinned, may be null
+    uint32_t *aux;          // kernel-seam mode: store 1 into aux[0..2], no ctrl
+    uint32_t *flags_dev;    // NCCL path: this rank's {range, inf, nan} as 0/1
+};
+
+// ---------------------------------------------------------------- memory ops
+
+__device__ __forceinline__ uint4 ld_stream(const void *p)
+{
+    return __ldcs(reinterpret_cast<const uint4 *>(p));
+}
+__device__ __forceinline__ void st_stream(void *p, uint4 v)
+{
+    __stcs(reinterpret_cast<uint4 *>(p), v);
+}
+// Load that always goes to the point of coherence of the owning GPU.
+__device__ __forceinline__ uint4 ld_peer(const void *p)
+{
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v)
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];"
+                 : "=r"(v)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Waits until *p has reached `epoch`.  Gives up after timeout_ns and returns
+// false; never spins without a limit.
+__device__ __forceinline__ bool wait_epoch(const uint32_t *p, uint32_t epoch,
+                                           unsigned long long timeout_ns)
+{
+    if((int32_t)(ld_acquire_sys(p) - epoch) >= 0)
+        return true;
+    const unsigned long long t0 = globaltimer_ns();
+    unsigned spins = 0;
+    for(;;) {
+        if((int32_t)(ld_acquire_sys(p) - epoch) >= 0)
+            return true;
+        __nanosleep(64);
+        if((++spins & 63u) == 0 && globaltimer_ns() - t0 > timeout_ns)
+            return false;
+    }
+}
+
+// ---------------------------------------------------------------- arithmetic
+
+// One element of the update, written in the order of the reference's source
+// (src/cuda/cuda_kernels.cu:177-187,212-228).
+__device__ __forceinline__ void adam_element(float dw, float &m, float &v,
+                                             float &w, float b1t, float b2t,
+                                             float lr, float lambda)
+{
+    const float b1 = B200OPT_ADAM_B1;
+    const float b2 = B200OPT_ADAM_B2;
+    const float e = B200OPT_ADAM_EPS;
+    m = b1 * m + (1.0f - b1) * dw;
+    v = b2 * v + (1.0f - b2) * dw * dw;
+    const float m_hat = m * b1t;
+    const float v_hat = v * b2t;
+    w = w - lr * m_hat * __frsqrt_rn(v_hat + e) - lr * lambda * w;
+}
+
+// Overflow classes of an fp16 bit pattern (src/cuda/cuda_kernels.cu:198-210).
+// Returns true when the element must be skipped.
+__device__ __forceinline__ bool classify_half(uint32_t u16, uint32_t &fl)
+{
+    if((u16 & 0x7800u) == 0x7800u) {
+        fl |= kFlagRange;
+        if((u16 & 0x7c00u) == 0x7c00u) {
+            fl |= (u16 & 0x3ffu) ? kFlagNan : kFlagInf;
+            return true;
+        }
+    }
+    return false;
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint32_t u16)
+{
+    return __half2float(__ushort_as_half((unsigned short)u16));
+}
+__device__ __forceinline__ uint32_t float_to_half_bits(float f)
+{
+    return (uint32_t)__half_as_ushort(__float2half_rn(f));
+}
+
+// ------------------------------------------------------ fp16 group, 8 elements
+
+template <int NR>
+struct HalfLoads {
+    uint4 g[NR];
+    uint4 m0, m1, v0, v1, c0, c1;
+};
+
+template <int NR>
+__device__ __forceinline__ void half_load(const StepParams &p, size_t idx0,
+                                          HalfLoads<NR> &L)
+{
+    const size_t li = idx0 - p.h.A;
+#pragma unroll
+    for(int q = 0; q < NR; q++) {
+        if(NR == 1)
+            L.g[q] = ld_stream(p.h.G[q] + idx0);
+        else
+            L.g[q] = ld_peer(p.h.G[q] + idx0);
+    }
+    L.m0 = ld_stream(p.h.m + li);
+    L.m1 = ld_stream(p.h.m + li + 4);
+    L.v0 = ld_stream(p.h.v + li);
+    L.v1 = ld_stream(p.h.v + li + 4);
+    L.c0 = ld_stream(p.h.c + li);
+    L.c1 = ld_stream(p.h.c + li + 4);
+}
+
+__device__ __forceinline__ void unpack8(const uint4 &a, const uint4 &b,
+                                        float (&x)[8])
+{
+    x[0] = __uint_as_float(a.x);
+    x[1] = __uint_as_float(a.y);
+    x[2] = __uint_as_float(a.z);
+    x[3] = __uint_as_float(a.w);
+    x[4] = __uint_as_float(b.x);
+    x[5] = __uint_as_float(b.y);
+    x[6] = __uint_as_float(b.z);
+    x[7] = __uint_as_float(b.w);
+}
+__device__ __forceinline__ void pack8(const float (&x)[8], uint4 &a, uint4 &b)
+{
+    a = make_uint4(__float_as_uint(x[0]), __float_as_uint(x[1]),
+                   __float_as_uint(x[2]), __float_as_uint(x[3]));
+    b = make_uint4(__float_as_uint(x[4]), __float_as_uint(x[5]),
+                   __float_as_uint(x[6]), __float_as_uint(x[7]));
+}
+__device__ __forceinline__ void halves8(const uint4 &g, uint32_t (&u)[8])
+{
+    u[0] = g.x & 0xffffu;
+    u[1] = g.x >> 16;
+    u[2] = g.y & 0xffffu;
+    u[3] = g.y >> 16;
+    u[4] = g.z & 0xffffu;
+    u[5] = g.z >> 16;
+    u[6] = g.w & 0xffffu;
+    u[7] = g.w >> 16;
+}
+
+template <int NR>
+__device__ __forceinline__ void half_compute_store(const StepParams &p,
+                                                   size_t idx0,
+                                                   const HalfLoads<NR> &L,
+                                                   uint32_t &fl)
+{
+    uint32_t u[8];
+    halves8(L.g[0], u);
+    if(NR > 1) {
+        // fp32 accumulation in rank order, one rounding to fp16
+        float acc[8];
+#pragma unroll
+        for(int e = 0; e < 8; e++)
+            acc[e] = half_bits_to_float(u[e]);
+#pragma unroll
+        for(int q = 1; q < NR; q++) {
+            uint32_t t[8];
+            halves8(L.g[q], t);
+#pragma unroll
+            for(int e = 0; e < 8; e++)
+                acc[e] += half_bits_to_float(t[e]);
+        }
+#pragma unroll
+        for(int e = 0; e < 8; e++)
+            u[e] = float_to_half_bits(acc[e]);
+    }
+
+    float m[8], v[8], c[8];
+    unpack8(L.m0, L.m1, m);
+    unpack8(L.v0, L.v1, v);
+    unpack8(L.c0, L.c1, c);
+
+    uint32_t skipped = 0;
+    uint32_t wbits[8];
+#pragma unroll
+    for(int e = 0; e < 8; e++) {
+        if(classify_half(u[e], fl)) {
+            skipped |= 1u << e;
+            wbits[e] = 0;
+        } else {
+            const float dw = half_bits_to_float(u[e]) * p.alpha;
+            adam_element(dw, m[e], v[e], c[e], p.b1t, p.b2t, p.lr, p.l2);
+            wbits[e] = float_to_half_bits(c[e]);
+        }
+    }
+    if(skipped) {
+        // a skipped element keeps its fp16 weight: fetch what the owner holds
+        const uint16_t *wold = p.h.W[p.rank] + idx0;
+#pragma unroll
+        for(int e = 0; e < 8; e++)
+            if(skipped & (1u << e))
+                wbits[e] = wold[e];
+    }
+
+    const size_t li = idx0 - p.h.A;
+    uint4 a, b;
+    pack8(m, a, b);
+    st_stream(p.h.m + li, a);
+    st_stream(p.h.m + li + 4, b);
+    pack8(v, a, b);
+    st_stream(p.h.v + li, a);
+    st_stream(p.h.v + li + 4, b);
+    pack8(c, a, b);
+    st_stream(p.h.c + li, a);
+    st_stream(p.h.c + li + 4, b);
+
+    const uint4 wv = make_uint4(wbits[0] | (wbits[1] << 16),
+                                wbits[2] | (wbits[3] << 16),
+                                wbits[4] | (wbits[5] << 16),
+                                wbits[6] | (wbits[7] << 16));
+#pragma unroll
+    for(int q = 0; q < NR; q++)
+        *reinterpret_cast<uint4 *>(p.h.W[q] + idx0) = wv;
+}
+
+// Element-wise path for the (at most two) groups that straddle a shard edge,
+// and for unaligned caller memory in kernel-seam mode.
+template <int NR>
+__device__ __noinline__ uint32_t half_scalar(const StepParams &p, size_t idx0)
+{
+    uint32_t fl = 0;
+    for(int e = 0; e < kVec; e++) {
+        const size_t i = idx0 + e;
+        if(i < p.h.o || i >= p.h.o + p.h.s)
+            continue;
+        uint32_t u = *reinterpret_cast<const volatile uint16_t *>(p.h.G[0] + i);
+        if(NR > 1) {
+            float acc = half_bits_to_float(u);
+            for(int q = 1; q < NR; q++)
+                acc += half_bits_to_float(
+                    *reinterpret_cast<const volatile uint16_t *>(p.h.G[q] + i));
+            u = float_to_half_bits(acc);
+        }
+        if(classify_half(u, fl))
+            continue;
+        const size_t li = i - p.h.A;
+        float m = p.h.m[li], v = p.h.v[li], c = p.h.c[li];
+        const float dw = half_bits_to_float(u) * p.alpha;
+        adam_element(dw, m, v, c, p.b1t, p.b2t, p.lr, p.l2);
+        p.h.m[li] = m;
+        p.h.v[li] = v;
+        p.h.c[li] = c;
+        const uint16_t wb = (uint16_t)float_to_half_bits(c);
+        for(int q = 0; q < NR; q++)
+            p.h.W[q][i] = wb;
+    }
+    return fl;
+}
+
+// ------------------------------------------------------ fp32 group, 8 elements
+
+template <int NR>
+struct FloatLoads {
+    uint4 g0[NR], g1[NR];
+    uint4 w0, w1, m0, m1, v0, v1;
+};
+
+template <int NR>
+__device__ __forceinline__ void float_load(const StepParams &p, size_t idx0,
+                                           FloatLoads<NR> &L)
+{
+    const size_t li = idx0 - p.f.A;
+#pragma unroll
+    for(int q = 0; q < NR; q++) {
+        if(NR == 1) {
+            L.g0[q] = ld_stream(p.f.G[q] + idx0);
+            L.g1[q] = ld_stream(p.f.G[q] + idx0 + 4);
+        } else {
+            L.g0[q] = ld_peer(p.f.G[q] + idx0);
+            L.g1[q] = ld_peer(p.f.G[q] + idx0 + 4);
+        }
+    }
+    L.w0 = ld_stream(p.f.W[p.rank] + idx0);
+    L.w1 = ld_stream(p.f.W[p.rank] + idx0 + 4);
+    L.m0 = ld_stream(p.f.m + li);
+    L.m1 = ld_stream(p.f.m + li + 4);
+    L.v0 = ld_stream(p.f.v + li);
+    L.v1 = ld_stream(p.f.v + li + 4);
+}
+
+// Non-finite classes of an fp32 gradient (src/cuda/cuda_kernels.cu:166-175):
+// no range flag in this group.
+__device__ __forceinline__ bool classify_float(float dw, uint32_t &fl)
+{
+    if(!isfinite(dw)) {
+        fl |= isnan(dw) ? kFlagNan : kFlagInf;
+        return true;
+    }
+    return false;
+}
+
+template <int NR>
+__device__ __forceinline__ void float_compute_store(const StepParams &p,
+                                                    size_t idx0,
+                                                    const FloatLoads<NR> &L,
+                                                    uint32_t &fl)
+{
+    float g[8], w[8], m[8], v[8];
+    unpack8(L.g0[0], L.g1[0], g);
+#pragma unroll
+    for(int q = 1; q < NR; q++) {
+        float t[8];
+        unpack8(L.g0[q], L.g1[q], t);
+#pragma unroll
+        for(int e = 0; e < 8; e++)
+            g[e] += t[e];
+    }
+    unpack8(L.w0, L.w1, w);
+    unpack8(L.m0, L.m1, m);
+    unpack8(L.v0, L.v1, v);
+#pragma unroll
+    for(int e = 0; e < 8; e++) {
+        if(!classify_float(g[e], fl))
+            adam_element(g[e], m[e], v[e], w[e], p.b1t, p.b2t, p.lr, p.l2);
+    }
+    const size_t li = idx0 - p.f.A;
+    uint4 a, b;
+    pack8(m, a, b);
+    st_stream(p.f.m + li, a);
+    st_stream(p.f.m + li + 4, b);
+    pack8(v, a, b);
+    st_stream(p.f.v + li, a);
+    st_stream(p.f.v + li + 4, b);
+    pack8(w, a, b);
+#pragma unroll
+    for(int q = 0; q < NR; q++) {
+        *reinterpret_cast<uint4 *>(p.f.W[q] + idx0) = a;
+        *reinterpret_cast<uint4 *>(p.f.W[q] + idx0 + 4) = b;
+    }
+}
+
+template <int NR>
+__device__ __noinline__ uint32_t float_scalar(const StepParams &p, size_t idx0)
+{
+    uint32_t fl = 0;
+    for(int e = 0; e < kVec; e++) {
+        const size_t i = idx0 + e;
+        if(i < p.f.o || i >= p.f.o + p.f.s)
+            continue;
+        float g = *reinterpret_cast<const volatile float *>(p.f.G[0] + i);
+        for(int q = 1; q < NR; q++)
+            g += *reinterpret_cast<const volatile float *>(p.f.G[q] + i);
+        if(classify_float(g, fl))
+            continue;
+        const size_t li = i - p.f.A;
+        float m = p.f.m[li], v = p.f.v[li], w = p.f.W[p.rank][i];
+        adam_element(g, m, v, w, p.b1t, p.b2t, p.lr, p.l2);
+        p.f.m[li] = m;
+        p.f.v[li] = v;
+        for(int q = 0; q < NR; q++)
+            p.f.W[q][i] = w;
+    }
+    return fl;
+}
+
+// ------------------------------------------------------------- the step kernel
+
+// UNR groups per thread are loaded before any is computed, to keep enough
+// bytes in flight per SM.
+template <int NR, int UNR, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB)
+    fused_step_kernel(const __grid_constant__ StepParams p)
+{
+    __shared__ int s_flag;
+    const int tid = threadIdx.x;
+    Ctrl *const my = p.ctrl[p.rank];
+    int aborted = 0;
+
+    if(NR > 1 && p.barrier) {
+        // "my gradients are final": one CTA tells every peer (and itself)
+        if(blockIdx.x == 0 && tid < NR)
+            st_release_sys(&p.ctrl[tid]->ready[p.rank], p.epoch);
+        int bad = 0;
+        if(tid < NR) {
+            if(!wait_epoch(&my->ready[tid], p.epoch, p.timeout_ns)) {
+                bad = 1;
+                if(atomicCAS(&my->status, 0u, (uint32_t)(-B200OPT_ETIMEOUT)) ==
+                       0u &&
+                   p.host) {
+                    p.host->where = 1;
+                    p.host->peer = tid;
+                }
+            }
+        }
+        aborted = __syncthreads_or(bad);
+    }
+
+    uint32_t fl = 0;
+    if(!aborted) {
+        const size_t stride = (size_t)gridDim.x * kThreads * UNR;
+        // fp16 group
+        {
+            const size_t ng = p.h.ngroups;
+            const size_t lo = p.h.o, hi = p.h.o + p.h.s;
+            for(size_t base = (size_t)blockIdx.x * kThreads * UNR; base < ng;
+                base += stride) {
+                HalfLoads<NR> L[UNR];
+                bool full[UNR];
+#pragma unroll
+                for(int k = 0; k < UNR; k++) {
+                    const size_t gid = base + (size_t)k * kThreads + tid;
+                    const size_t idx0 = p.h.A + gid * kVec;
+                    full[k] = gid < ng && idx0 >= lo && idx0 + kVec <= hi &&
+                              !p.force_scalar;
+                    if(full[k])
+                        half_load<NR>(p, idx0, L[k]);
+                }
+#pragma unroll
+                for(int k = 0; k < UNR; k++) {
+                    const size_t gid = base + (size_t)k * kThreads + tid;
+                    const size_t idx0 = p.h.A + gid * kVec;
+                    if(full[k])
+                        half_compute_store<NR>(p, idx0, L[k], fl);
+                    else if(gid < ng)
+                        fl |= half_scalar<NR>(p, idx0);
+                }
+            }
+        }
+        // fp32 group
+        {
+            const size_t ng = p.f.ngroups;
+            const size_t lo = p.f.o, hi = p.f.o + p.f.s;
+            for(size_t base = (size_t)blockIdx.x * kThreads; base < ng;
+                base += (size_t)gridDim.x * kThreads) {
+                const size_t gid = base + tid;
+                const size_t idx0 = p.f.A + gid * kVec;
+                if(gid < ng) {
+                    if(idx0 >= lo && idx0 + kVec <= hi && !p.force_scalar) {
+                        FloatLoads<NR> L;
+                        float_load<NR>(p, idx0, L);
+                        float_compute_store<NR>(p, idx0, L, fl);
+                    } else {
+                        fl |= float_scalar<NR>(p, idx0);
+                    }
+                }
+            }
+        }
+    }
+
+    // one flag word per warp, then at most one atomic per warp that saw any
+    fl = __reduce_or_sync(0xffffffffu, fl);
+
+    if(p.aux) {
+        // kernel-seam mode: the reference's plain stores of 1 into CudaAux
+        if((tid & 31) == 0 && fl) {
+            if(fl & kFlagRange)
+                p.aux[0] = 1;
+            if(fl & kFlagInf)
+                p.aux[1] = 1;
+            if(fl & kFlagNan)
+                p.aux[2] = 1;
+        }
+        return;
+    }
+
+    if((tid & 31) == 0 && fl)
+        atomicOr(&my->local_flags, fl);
+
+    // completion: the last CTA of this launch finishes the step
+    if(NR > 1)
+        __threadfence_system();  // weight stores into peers before the signal
+    else
+        __threadfence();
+    __syncthreads();
+    if(tid == 0)
+        s_flag = atomicAdd(&my->cta_done, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if(!s_flag)
+        return;
+    __threadfence();
+
+    const uint32_t mine =
+        *reinterpret_cast<volatile uint32_t *>(&my->local_flags);
+    uint32_t status = *reinterpret_cast<volatile uint32_t *>(&my->status);
+    uint32_t sums[3] = {(mine & kFlagRange) ? 1u : 0u,
+                        (mine & kFlagInf) ? 1u : 0u,
+                        (mine & kFlagNan) ? 1u : 0u};
+    const int par = p.epoch & 1;
+
+    if(NR > 1) {
+        // publish this rank's flag word into every rank's slot array
+        if(tid < NR)
+            p.ctrl[tid]->flagword[par][p.rank] = mine | kFlagValid;
+        if(p.barrier && !status) {
+            int bad = 0;
+            if(tid < NR) {
+                __threadfence_system();
+                st_release_sys(&p.ctrl[tid]->done[p.rank], p.epoch);
+                if(!wait_epoch(&my->done[tid], p.epoch, p.timeout_ns)) {
+                    bad = 1;
+                    if(atomicCAS(&my->status, 0u,
+                                 (uint32_t)(-B200OPT_ETIMEOUT)) == 0u &&
+                       p.host) {
+                        p.host->where = 2;
+                        p.host->peer = tid;
+                    }
+                }
+            }
+            if(__syncthreads_or(bad))
+                status = (uint32_t)(-B200OPT_ETIMEOUT);
+            if(tid == 0 && !status) {
+                sums[0] = sums[1] = sums[2] = 0;
+                for(int q = 0; q < NR; q++) {
+                    const uint32_t w = *reinterpret_cast<volatile uint32_t *>(
+                        &my->flagword[par][q]);
+                    sums[0] += (w & kFlagRange) ? 1u : 0u;
+                    sums[1] += (w & kFlagInf) ? 1u : 0u;
+                    sums[2] += (w & kFlagNan) ? 1u : 0u;
+                }
+            }
+        }
+    }
+    if(tid == 0) {
+        if(p.flags_dev) {
+            p.flags_dev[0] = sums[0];
+            p.flags_dev[1] = sums[1];
+            p.flags_dev[2] = sums[2];
+        }
+        if(p.host) {
+            p.host->range = sums[0];
+            p.host->inf = sums[1];
+            p.host->nan = sums[2];
+            p.host->status = status;
+            p.host->epoch = p.epoch;
+        }
+        my->local_flags = 0;
+        my->cta_done = 0;
+        __threadfence_system();
+    }
+}
+
+// master := float(fp16 weights) over the shard (AdamMixed constructor,
+// src/cuda/cuda_optimizer.cpp:142-145); c is indexed like in the step kernel.
+__global__ void init_master_kernel(const uint16_t *w, float *c, size_t o,
+                                   size_t s, size_t A)
+{
+    for(size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < s;
+        i += (size_t)gridDim.x * blockDim.x)
+        c[o + i - A] = half_bits_to_float(w[o + i]);
+}
+
+}  // namespace b200
