@@ -197,10 +197,14 @@ orc_rsqrt_rn(float x)
 /* ------------------------------------------------------- Adam, one element */
 
 /* src/cuda/cuda_kernels.cu:177-187 and :212-228, same expression order.
- * w0 is the fp32 weight the update starts from (master copy or fp32 weight). */
+ * w0 is the fp32 weight the update starts from (master copy or fp32 weight).
+ * `mixed` selects which of the two reference kernels is being restated: nvcc
+ * contracts `b*x + (1-b)*dw` differently in the two (in adam_kernel_mp dw is
+ * itself a product, in adam_kernel it is a plain load), as the golden fixtures
+ * show bit for bit. */
 static inline void
 adam_update(float dw, float *m_io, float *v_io, float *w_io, float b1t,
-            float b2t, float lr, float lambda, int model)
+            float b2t, float lr, float lambda, int model, int mixed)
 {
     const float b1 = (float)0.9;
     const float b2 = (float)0.999;
@@ -216,12 +220,17 @@ adam_update(float dw, float *m_io, float *v_io, float *w_io, float b1t,
         const float v_hat = v * b2t;
         w = w - lr * m_hat * rsqrt_rn(v_hat + e) - lr * lambda * w;
     } else {
-        /* a*b + c*d contracts to fma(a, b, c*d);  x - a*b to fma(-a, b, x) */
-        m = fmaf(b1, *m_io, omb1 * dw);
-        v = fmaf(b2, *v_io, omb2 * dw * dw);
+        if(mixed) {
+            m = fmaf(b1, *m_io, omb1 * dw);
+            v = fmaf(b2, *v_io, omb2 * dw * dw);
+        } else {
+            m = fmaf(omb1, dw, b1 * *m_io);
+            v = fmaf(omb2 * dw, dw, b2 * *v_io);
+        }
+        /* v*b2t + e is one fma (v_hat never exists as a rounded value), and
+         * each x - a*b is fma(-a, b, x) */
         const float m_hat = m * b1t;
-        const float v_hat = v * b2t;
-        const float t = fmaf(-(lr * m_hat), rsqrt_rn(v_hat + e), w);
+        const float t = fmaf(-(lr * m_hat), rsqrt_rn(fmaf(v, b2t, e)), w);
         w = fmaf(-(lr * lambda), w, t);
     }
     *m_io = m;
@@ -251,7 +260,7 @@ orc_adam_mixed(size_t n, float alpha, uint16_t *w, const uint16_t *g, float *m,
             }
         }
         const float dw = orc_h2f(u) * alpha;
-        adam_update(dw, &m[i], &v[i], &c[i], b1t, b2t, lr, lambda, model);
+        adam_update(dw, &m[i], &v[i], &c[i], b1t, b2t, lr, lambda, model, 1);
         w[i] = orc_f2h(c[i]);
     }
 }
@@ -270,7 +279,7 @@ orc_adam_f32(size_t n, float *w, const float *g, float *m, float *v, float b1t,
                 flags[1] = 1;
             continue;
         }
-        adam_update(dw, &m[i], &v[i], &w[i], b1t, b2t, lr, lambda, model);
+        adam_update(dw, &m[i], &v[i], &w[i], b1t, b2t, lr, lambda, model, 0);
     }
 }
 
@@ -490,9 +499,8 @@ orc_adam_mixed_mt(size_t n, float alpha, uint16_t *w, const uint16_t *g,
         const float mi = fmaf(b1, m[i], omb1 * dw);
         const float vi = fmaf(b2, v[i], omb2 * dw * dw);
         const float m_hat = mi * b1t;
-        const float v_hat = vi * b2t;
         float wi = c[i];
-        const float r = (float)(1.0 / sqrt((double)(v_hat + e)));
+        const float r = rsqrt_rn(fmaf(vi, b2t, e));
         const float t = fmaf(-(lr * m_hat), r, wi);
         wi = fmaf(-(lr * lambda), wi, t);
         m[i] = mi;

@@ -158,8 +158,15 @@ __device__ __forceinline__ bool wait_epoch(const uint32_t *p, uint32_t epoch,
 
 // ---------------------------------------------------------------- arithmetic
 
-// One element of the update, written in the order of the reference's source
-// (src/cuda/cuda_kernels.cu:177-187,212-228).
+// One element of the update.  The reference writes it as plain expressions
+// (src/cuda/cuda_kernels.cu:177-187,212-228 of the Saga tree) and lets nvcc
+// contract multiply-add pairs; which pairs it fuses differs between the
+// reference's two kernels (in adam_kernel_mp the gradient is itself a product,
+// in adam_kernel a plain load).  The roundings are spelled out here with
+// intrinsics, one variant per reference kernel, so that the results equal the
+// compiled reference bit for bit whatever this file's surroundings make the
+// compiler prefer.
+template <bool MIXED>
 __device__ __forceinline__ void adam_element(float dw, float &m, float &v,
                                              float &w, float b1t, float b2t,
                                              float lr, float lambda)
@@ -167,11 +174,23 @@ __device__ __forceinline__ void adam_element(float dw, float &m, float &v,
     const float b1 = B200OPT_ADAM_B1;
     const float b2 = B200OPT_ADAM_B2;
     const float e = B200OPT_ADAM_EPS;
-    m = b1 * m + (1.0f - b1) * dw;
-    v = b2 * v + (1.0f - b2) * dw * dw;
-    const float m_hat = m * b1t;
-    const float v_hat = v * b2t;
-    w = w - lr * m_hat * __frsqrt_rn(v_hat + e) - lr * lambda * w;
+    const float omb1 = 1.0f - b1;
+    const float omb2 = 1.0f - b2;
+    if(MIXED) {
+        // m = b1*m + (1-b1)*dw ; v = b2*v + (1-b2)*dw*dw : left product fused
+        m = __fmaf_rn(b1, m, __fmul_rn(omb1, dw));
+        v = __fmaf_rn(b2, v, __fmul_rn(__fmul_rn(omb2, dw), dw));
+    } else {
+        // same source text, right product fused
+        m = __fmaf_rn(omb1, dw, __fmul_rn(b1, m));
+        v = __fmaf_rn(__fmul_rn(omb2, dw), dw, __fmul_rn(b2, v));
+    }
+    const float m_hat = __fmul_rn(m, b1t);
+    // v_hat + e is a single fma: v_hat = v*b2t is never rounded on its own
+    const float r = __frsqrt_rn(__fmaf_rn(v, b2t, e));
+    // w - lr*m_hat*r - lr*lambda*w, each subtraction of a product one fma
+    const float t = __fmaf_rn(-__fmul_rn(lr, m_hat), r, w);
+    w = __fmaf_rn(-__fmul_rn(lr, lambda), w, t);
 }
 
 // Overflow classes of an fp16 bit pattern (src/cuda/cuda_kernels.cu:198-210).
@@ -296,8 +315,8 @@ __device__ __forceinline__ void half_compute_store(const StepParams &p,
             skipped |= 1u << e;
             wbits[e] = 0;
         } else {
-            const float dw = half_bits_to_float(u[e]) * p.alpha;
-            adam_element(dw, m[e], v[e], c[e], p.b1t, p.b2t, p.lr, p.l2);
+            const float dw = __fmul_rn(half_bits_to_float(u[e]), p.alpha);
+            adam_element<true>(dw, m[e], v[e], c[e], p.b1t, p.b2t, p.lr, p.l2);
             wbits[e] = float_to_half_bits(c[e]);
         }
     }
@@ -353,8 +372,8 @@ __device__ __noinline__ uint32_t half_scalar(const StepParams &p, size_t idx0)
             continue;
         const size_t li = i - p.h.A;
         float m = p.h.m[li], v = p.h.v[li], c = p.h.c[li];
-        const float dw = half_bits_to_float(u) * p.alpha;
-        adam_element(dw, m, v, c, p.b1t, p.b2t, p.lr, p.l2);
+        const float dw = __fmul_rn(half_bits_to_float(u), p.alpha);
+        adam_element<true>(dw, m, v, c, p.b1t, p.b2t, p.lr, p.l2);
         p.h.m[li] = m;
         p.h.v[li] = v;
         p.h.c[li] = c;
@@ -429,7 +448,7 @@ __device__ __forceinline__ void float_compute_store(const StepParams &p,
 #pragma unroll
     for(int e = 0; e < 8; e++) {
         if(!classify_float(g[e], fl))
-            adam_element(g[e], m[e], v[e], w[e], p.b1t, p.b2t, p.lr, p.l2);
+            adam_element<false>(g[e], m[e], v[e], w[e], p.b1t, p.b2t, p.lr, p.l2);
     }
     const size_t li = idx0 - p.f.A;
     uint4 a, b;
@@ -462,7 +481,7 @@ __device__ __noinline__ uint32_t float_scalar(const StepParams &p, size_t idx0)
             continue;
         const size_t li = i - p.f.A;
         float m = p.f.m[li], v = p.f.v[li], w = p.f.W[p.rank][i];
-        adam_element(g, m, v, w, p.b1t, p.b2t, p.lr, p.l2);
+        adam_element<false>(g, m, v, w, p.b1t, p.b2t, p.lr, p.l2);
         p.f.m[li] = m;
         p.f.v[li] = v;
         for(int q = 0; q < NR; q++)

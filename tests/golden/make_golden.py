@@ -127,11 +127,13 @@ def main():
         run_mixed("adam_mixed_n4112", 4112, 6, 1e-3, 0.01, 1024.0, 3, seed=11),
         run_mixed("adam_mixed_n272_l2zero", 272, 4, 1e-2, 0.0, 64.0, 2, seed=12),
         run_mixed("adam_mixed_n16", 16, 3, 1e-3, 0.01, 256.0, 0, seed=13),
+        run_mixed("adam_mixed_n1040_big_decay", 1040, 4, 0.05, 0.5, 64.0, 2, seed=15),
     ):
         np.savez_compressed(os.path.join(outdir, name + ".npz"), **out)
         report[name] = {f"oracle_model{k}": compare_with_oracle(out, k) for k in (0, 1)}
-    name, out = run_float("adam_float_n1040", 1040, 4, 1e-3, 0.01, seed=14)
-    np.savez_compressed(os.path.join(outdir, name + ".npz"), **out)
+    for name, out in (run_float("adam_float_n1040", 1040, 4, 1e-3, 0.01, seed=14),
+                      run_float("adam_float_n528_big_decay", 528, 4, 0.05, 0.5, seed=16)):
+        np.savez_compressed(os.path.join(outdir, name + ".npz"), **out)
     with open(os.path.join(outdir, "report.json"), "w") as f:
         json.dump(report, f, indent=1)
     print(json.dumps(report, indent=1))

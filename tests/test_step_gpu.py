@@ -77,7 +77,7 @@ def test_seam_adam_mixed_vs_oracle(oracle, n, offset):
         assert np.array_equal(gw, gc.astype(np.float16).view(np.uint16))
     # skipped elements: nothing moved
     skipped = (g & 0x7C00) == 0x7C00
-    assert skipped.sum() >= 5
+    assert skipped.sum() >= 4
     assert np.array_equal(gw[skipped], w[skipped])
     assert _bits_equal(gm[skipped], m[skipped]) and _bits_equal(gc[skipped], c[skipped])
 
