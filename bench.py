@@ -32,6 +32,10 @@ LR, L2, SCALE0 = 1e-3, 0.01, 1024.0
 NVLINK_MEASURED_GBS = 770.0   # peer copy per direction measured on this pool
 NVLINK_NOMINAL_GBS = 900.0
 HBM_FALLBACK_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the default one-rank
+# kernel on this workload, from the ncu capture summarised in
+# profiles/staged_step_kernel_n1_config2.md
+NCU_TRAFFIC_N1_BYTES = 660_591_104
 
 
 def measured_peaks():
@@ -108,7 +112,7 @@ class ClockSampler:
 
 # ----------------------------------------------------------- CPU baseline leg
 
-def cpu_baseline(n, budget_s=12.0, max_steps=400):
+def cpu_baseline(n, budget_s=12.0, max_steps=5000):
     """The CPU restatement of the reference's adam_kernel_mp (the reference has
     no CPU implementation of this path), all host threads, on the full buffer."""
     from oracle import oracle as orc
@@ -196,6 +200,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ctas-per-sm", type=int, default=0)
     ap.add_argument("--variant", type=int, default=-1)
+    ap.add_argument("--stages", type=int, default=0)
+    ap.add_argument("--grid", type=int, default=0)
     ap.add_argument("--path", default="auto", choices=["auto", "peer", "nccl"])
     args = ap.parse_args()
     if args.impl == "reference":
@@ -245,6 +251,10 @@ def main():
         grp.set_option(capi.OPT_CTAS_PER_SM, args.ctas_per_sm)
     if args.variant >= 0:
         grp.set_option(capi.OPT_KERNEL_VARIANT, args.variant)
+    if args.stages:
+        grp.set_option(capi.OPT_STAGES, args.stages)
+    if args.grid:
+        grp.set_option(capi.OPT_GRID, args.grid)
 
     stream = torch.cuda.current_stream(dev)
     sp = stream.cuda_stream
@@ -333,7 +343,8 @@ def main():
             },
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                "frac": achieved / hbm_peak, "traffic": None,
+                "frac": achieved / hbm_peak,
+                "traffic": NCU_TRAFFIC_N1_BYTES if (world == 1 and not args.params) else None,
                 "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": alg_bytes,
                 "frac_of_8000_nominal": achieved / 8000.0,
             },

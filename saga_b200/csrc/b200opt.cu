@@ -4,12 +4,15 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
 
 #include "fused_step.cuh"
+#include "staged_step.cuh"
 #include "nccl_path.h"
 
 using namespace b200;
@@ -38,6 +41,8 @@ struct b200opt {
     // local state
     float *mh = nullptr, *vh = nullptr, *ch = nullptr, *mf = nullptr,
           *vf = nullptr;
+    char *state = nullptr;  // one allocation holding the five arrays above
+    size_t state_bytes = 0;
     size_t state_h_elems = 0, state_f_elems = 0;
     HostResult *host = nullptr;      // pinned + mapped
     HostResult *host_dev = nullptr;  // device alias of `host`
@@ -50,6 +55,8 @@ struct b200opt {
     long path = B200OPT_PATH_AUTO;
     long ctas_per_sm = 0;  // 0 = built-in default
     long variant = 0;
+    long stages = 0;
+    long grid = 0;
     long nccl_crossover = 0;
     uint64_t launches = 0;
     NcclPath *nccl = nullptr;
@@ -132,24 +139,104 @@ cudaError_t launch_variant(const StepParams &p, int grid, cudaStream_t st)
     return cudaGetLastError();
 }
 
+// Tuning knobs of a launch (0 = the variant's default).
+struct LaunchTuning {
+    long ctas_per_sm = 0;
+    long variant = 0;
+    long stages = 0;
+    long grid = 0;
+};
+
+template <int NR, int VEC, int THREADS>
+cudaError_t launch_staged(StepParams p, int num_sms, const LaunchTuning &t,
+                          int def_stages, int def_ctas, cudaStream_t st)
+{
+    constexpr int TILE = THREADS * VEC;
+    constexpr size_t per_stage = stage_bytes(NR, TILE);
+    const size_t budget = 227 * 1024 - 1024;
+    const long cps = t.ctas_per_sm > 0 ? t.ctas_per_sm : def_ctas;
+    int stages = (int)(t.stages > 0 ? t.stages : def_stages);
+    // the rings of all CTAs resident on an SM must fit its shared memory
+    while(stages > 1 && (size_t)stages * per_stage * (size_t)cps > budget)
+        stages--;
+    if(stages > kMaxStages)
+        stages = kMaxStages;
+    const size_t smem = (size_t)stages * per_stage;
+    if(smem > budget)
+        return cudaErrorInvalidValue;
+    auto kern = staged_step_kernel<NR, VEC, THREADS>;
+    // opting in to large dynamic shared memory is per device and sticky
+    static std::atomic<uint64_t> opted{0};
+    int dev = 0;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if(ce != cudaSuccess)
+        return ce;
+    if(dev >= 64 || !(opted.load() & (1ull << dev))) {
+        ce = cudaFuncSetAttribute(
+            kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+        if(ce != cudaSuccess)
+            return ce;
+        if(dev < 64)
+            opted.fetch_or(1ull << dev);
+    }
+    const size_t tiles_h = (p.h.ngroups * kVec + TILE - 1) / TILE;
+    const size_t tiles_f = (p.f.ngroups + THREADS - 1) / THREADS;
+    size_t want = std::max<size_t>(std::max(tiles_h, tiles_f), 1);
+    const size_t cap = t.grid > 0 ? (size_t)t.grid : (size_t)num_sms * cps;
+    const int grid = (int)std::min<size_t>(want, cap);
+    p.stages = stages;
+    kern<<<grid, THREADS, smem, st>>>(p);
+    return cudaGetLastError();
+}
+
 // Launch shape: a persistent grid of ctas_per_sm CTAs on every SM, shrunk for
 // small inputs so that no CTA starts without work.
-//   variant 0: one 8-element group per thread per trip
-//   variant 1: two groups per thread per trip (one rank only)
+//   variant 0: the default of the rank count (4 for one rank)
+//   variant 1: direct loads, one 8-element group per thread per trip
+//   variants 2..5: bulk-copy staging through shared memory
+//     2: 256 threads x 8 elements   3: 128 threads x 8 elements
+//     4: 256 threads x 4 elements   5: 512 threads x 4 elements
+//   variant 6: direct loads, two groups per thread per trip (one rank only)
+// Measured on a B200 at 25.6 M fp16 parameters, one rank: variant 4 with two
+// CTAs per SM and four stages 114.9 us; best direct-load shape 119.4 us.
 cudaError_t launch_step(const StepParams &p, int nranks, int num_sms,
-                        long ctas_per_sm, long variant, cudaStream_t st)
+                        const LaunchTuning &t, cudaStream_t st)
 {
+    const long variant = t.variant > 0 ? t.variant : (nranks == 1 ? 4 : 1);
+    const long ctas_per_sm = t.ctas_per_sm;
+#define STAGED(NR)                                                         \
+    switch(variant) {                                                      \
+    case 2: return launch_staged<NR, 8, 256>(p, num_sms, t, 4, 2, st);     \
+    case 3: return launch_staged<NR, 8, 128>(p, num_sms, t, 4, 4, st);     \
+    case 4: return launch_staged<NR, 4, 256>(p, num_sms, t, 4, 2, st);     \
+    default: return launch_staged<NR, 4, 512>(p, num_sms, t, 4, 1, st);    \
+    }
+    if(variant >= 2 && variant <= 5) {
+        switch(nranks) {
+        case 1: STAGED(1)
+        case 2: STAGED(2)
+        case 3: STAGED(3)
+        case 4: STAGED(4)
+        case 5: STAGED(5)
+        case 6: STAGED(6)
+        case 7: STAGED(7)
+        case 8: STAGED(8)
+        }
+        return cudaErrorInvalidValue;
+    }
+#undef STAGED
     const size_t groups = std::max(p.h.ngroups, p.f.ngroups);
-    const int unr = (nranks == 1 && variant == 1) ? 2 : 1;
-    const long def_ctas = nranks == 1 ? (variant == 1 ? 2 : 3) : 2;
+    const int unr = (nranks == 1 && variant == 6) ? 2 : 1;
+    const long def_ctas = 2;
     const long cps = ctas_per_sm > 0 ? ctas_per_sm : def_ctas;
     size_t want = (groups + (size_t)kThreads * unr - 1) / ((size_t)kThreads * unr);
     if(want == 0)
         want = 1;
-    const int grid = (int)std::min<size_t>(want, (size_t)num_sms * cps);
+    const int grid = (int)std::min<size_t>(
+        want, t.grid > 0 ? (size_t)t.grid : (size_t)num_sms * cps);
     switch(nranks) {
     case 1:
-        return variant == 1 ? launch_variant<1, 2, 2>(p, grid, st)
+        return variant == 6 ? launch_variant<1, 2, 2>(p, grid, st)
                             : launch_variant<1, 1, 3>(p, grid, st);
     case 2: return launch_variant<2, 1, 3>(p, grid, st);
     case 3: return launch_variant<3, 1, 2>(p, grid, st);
@@ -160,6 +247,22 @@ cudaError_t launch_step(const StepParams &p, int nranks, int num_sms,
     case 8: return launch_variant<8, 1, 2>(p, grid, st);
     }
     return cudaErrorInvalidValue;
+}
+
+LaunchTuning tuning_of(const b200opt *h)
+{
+    LaunchTuning t;
+    t.ctas_per_sm = h->ctas_per_sm;
+    t.variant = h->variant;
+    t.stages = h->stages;
+    t.grid = h->grid;
+    return t;
+}
+
+LaunchTuning seam_tuning()
+{
+    LaunchTuning t;
+    return t;
 }
 
 bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
@@ -250,30 +353,33 @@ int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
         // array
         h->state_h_elems = h->sh ? round_up(h->oh + h->sh - h->Ah, kVec) : 0;
         h->state_f_elems = h->sf ? round_up(h->of + h->sf - h->Af, kVec) : 0;
-        float **hs[3] = {&h->mh, &h->vh, &h->ch};
-        for(auto pp : hs) {
-            if(!h->state_h_elems)
-                continue;
-            if((ce = cudaMalloc(pp, h->state_h_elems * 4)) != cudaSuccess) {
-                rc = B200OPT_ENOMEM;
-                break;
+        // one allocation for all shard state: [m | v | master | m32 | v32]
+        {
+            const size_t skew = 0;
+            const size_t hb = round_up(h->state_h_elems * 4, 256);
+            const size_t fb = round_up(h->state_f_elems * 4, 256);
+            const size_t hstride = hb ? hb + skew : 0;
+            h->state_bytes = 3 * hstride + 2 * fb;
+            if(h->state_bytes) {
+                if((ce = cudaMalloc(&h->state, h->state_bytes)) != cudaSuccess) {
+                    rc = B200OPT_ENOMEM;
+                    break;
+                }
+                if((ce = cudaMemset(h->state, 0, h->state_bytes)) != cudaSuccess) {
+                    rc = B200OPT_ECUDA;
+                    break;
+                }
+                if(hb) {
+                    h->mh = (float *)(h->state);
+                    h->vh = (float *)(h->state + hstride);
+                    h->ch = (float *)(h->state + 2 * hstride);
+                }
+                if(fb) {
+                    h->mf = (float *)(h->state + 3 * hstride);
+                    h->vf = (float *)(h->state + 3 * hstride + fb);
+                }
             }
-            cudaMemset(*pp, 0, h->state_h_elems * 4);
         }
-        if(rc)
-            break;
-        float **fs[2] = {&h->mf, &h->vf};
-        for(auto pp : fs) {
-            if(!h->state_f_elems)
-                continue;
-            if((ce = cudaMalloc(pp, h->state_f_elems * 4)) != cudaSuccess) {
-                rc = B200OPT_ENOMEM;
-                break;
-            }
-            cudaMemset(*pp, 0, h->state_f_elems * 4);
-        }
-        if(rc)
-            break;
         if((ce = cudaHostAlloc(&h->host, sizeof(HostResult),
                                cudaHostAllocMapped | cudaHostAllocPortable)) !=
            cudaSuccess) {
@@ -315,11 +421,7 @@ int b200opt_destroy(b200opt_t *h)
             cudaIpcCloseMemHandle(h->peer_arena[q]);
     }
     cudaFree(h->arena);
-    cudaFree(h->mh);
-    cudaFree(h->vh);
-    cudaFree(h->ch);
-    cudaFree(h->mf);
-    cudaFree(h->vf);
+    cudaFree(h->state);
     if(h->host)
         cudaFreeHost(h->host);
     delete h;
@@ -544,7 +646,7 @@ int b200opt_step(b200opt_t *h, float lr, float l2_lambda, float scale,
         p.host = nullptr;
         p.flags_dev = ctrl->coll_flags;
         p.barrier = 0;
-        CK(h, launch_step(p, 1, h->num_sms, h->ctas_per_sm, h->variant, st));
+        CK(h, launch_step(p, 1, h->num_sms, tuning_of(h), st));
         rc = nccl_path_all_gather_and_flags(h->nccl, wh, h->sh, wf, h->sf,
                                             ctrl->coll_flags, st, &err);
         if(rc)
@@ -557,7 +659,7 @@ int b200opt_step(b200opt_t *h, float lr, float l2_lambda, float scale,
 
     fill_groups(h, p);
     p.barrier = (h->nranks > 1 && !h->serial) ? 1 : 0;
-    CK(h, launch_step(p, h->nranks, h->num_sms, h->ctas_per_sm, h->variant, st));
+    CK(h, launch_step(p, h->nranks, h->num_sms, tuning_of(h), st));
     h->launches++;
     return B200OPT_OK;
 }
@@ -654,9 +756,10 @@ int b200opt_adam_mixed(size_t n, float alpha, void *weights,
     p.lr = learning_rate;
     p.l2 = l2_lambda;
     p.aux = aux;
+    p.timeout_ns = 10000000000ull;
     p.force_scalar = !(aligned16(weights) && aligned16(gradients) &&
                        aligned16(mvec) && aligned16(vvec) && aligned16(cvec));
-    return launch_step(p, 1, sms, 0, 0, (cudaStream_t)stream) == cudaSuccess
+    return launch_step(p, 1, sms, seam_tuning(), (cudaStream_t)stream) == cudaSuccess
                ? B200OPT_OK
                : B200OPT_ECUDA;
 }
@@ -688,9 +791,10 @@ int b200opt_adam_float(size_t n, float *weights, const float *gradients,
     p.lr = learning_rate;
     p.l2 = l2_lambda;
     p.aux = aux;
+    p.timeout_ns = 10000000000ull;
     p.force_scalar = !(aligned16(weights) && aligned16(gradients) &&
                        aligned16(mvec) && aligned16(vvec));
-    return launch_step(p, 1, sms, 0, 0, (cudaStream_t)stream) == cudaSuccess
+    return launch_step(p, 1, sms, seam_tuning(), (cudaStream_t)stream) == cudaSuccess
                ? B200OPT_OK
                : B200OPT_ECUDA;
 }
@@ -797,7 +901,7 @@ int b200opt_set_option(b200opt_t *h, int option, long value)
         h->ctas_per_sm = value;
         return B200OPT_OK;
     case B200OPT_OPT_KERNEL_VARIANT:
-        if(value < 0 || value > 1)
+        if(value < 0 || value > 6)
             return B200OPT_EINVAL;
         h->variant = value;
         return B200OPT_OK;
@@ -805,6 +909,16 @@ int b200opt_set_option(b200opt_t *h, int option, long value)
         if(value < 0)
             return B200OPT_EINVAL;
         h->nccl_crossover = value;
+        return B200OPT_OK;
+    case B200OPT_OPT_STAGES:
+        if(value < 0 || value > 16)
+            return B200OPT_EINVAL;
+        h->stages = value;
+        return B200OPT_OK;
+    case B200OPT_OPT_GRID:
+        if(value < 0 || value > 65535)
+            return B200OPT_EINVAL;
+        h->grid = value;
         return B200OPT_OK;
     }
     return B200OPT_EINVAL;
@@ -820,6 +934,8 @@ int b200opt_get_option(const b200opt_t *h, int option, long *value)
     case B200OPT_OPT_CTAS_PER_SM: *value = h->ctas_per_sm; return B200OPT_OK;
     case B200OPT_OPT_KERNEL_VARIANT: *value = h->variant; return B200OPT_OK;
     case B200OPT_OPT_NCCL_CROSSOVER: *value = h->nccl_crossover; return B200OPT_OK;
+    case B200OPT_OPT_STAGES: *value = h->stages; return B200OPT_OK;
+    case B200OPT_OPT_GRID: *value = h->grid; return B200OPT_OK;
     }
     return B200OPT_EINVAL;
 }

@@ -89,6 +89,7 @@ struct StepParams {
     int rank;
     int barrier;      // 1: wait for peers inside the kernel
     int force_scalar; // 1: pointers are not 16-byte aligned, element-wise path
+    int stages;       // staged kernel: depth of the shared-memory ring
     uint32_t epoch;
     unsigned long long timeout_ns;
     Ctrl *ctrl[kMaxRanks];  // control block of every rank (ctrl[rank] local)
@@ -216,6 +217,45 @@ __device__ __forceinline__ uint32_t float_to_half_bits(float f)
     return (uint32_t)__half_as_ushort(__float2half_rn(f));
 }
 
+// Classifies and updates VEC elements whose reduced gradient bit patterns are
+// u[].  Nearly every group holds no value of magnitude >= 32768: that is
+// tested once for the whole group, and the common case then runs the VEC
+// independent update chains without a branch between them.  wold points at
+// the owner's current fp16 weights of these elements (read only when an
+// element is skipped and must keep its weight).
+template <int VEC>
+__device__ __forceinline__ void half_update(const StepParams &p,
+                                            const uint32_t (&u)[VEC],
+                                            float (&m)[VEC], float (&v)[VEC],
+                                            float (&c)[VEC],
+                                            uint32_t (&wbits)[VEC],
+                                            const uint16_t *wold, uint32_t &fl)
+{
+    bool any = false;
+#pragma unroll
+    for(int e = 0; e < VEC; e++)
+        any |= (u[e] & 0x7800u) == 0x7800u;
+    if(!any) {
+#pragma unroll
+        for(int e = 0; e < VEC; e++) {
+            const float dw = __fmul_rn(half_bits_to_float(u[e]), p.alpha);
+            adam_element<true>(dw, m[e], v[e], c[e], p.b1t, p.b2t, p.lr, p.l2);
+            wbits[e] = float_to_half_bits(c[e]);
+        }
+        return;
+    }
+#pragma unroll
+    for(int e = 0; e < VEC; e++) {
+        if(classify_half(u[e], fl)) {
+            wbits[e] = wold[e];  // skipped: m, v, master and weight stay
+        } else {
+            const float dw = __fmul_rn(half_bits_to_float(u[e]), p.alpha);
+            adam_element<true>(dw, m[e], v[e], c[e], p.b1t, p.b2t, p.lr, p.l2);
+            wbits[e] = float_to_half_bits(c[e]);
+        }
+    }
+}
+
 // ------------------------------------------------------ fp16 group, 8 elements
 
 template <int NR>
@@ -275,11 +315,12 @@ __device__ __forceinline__ void halves8(const uint4 &g, uint32_t (&u)[8])
     u[7] = g.w >> 16;
 }
 
+// Reduces, classifies and updates one 8-element group held in registers.
+// out[0..1] = m, out[2..3] = v, out[4..5] = master, out[6] = fp16 weights.
 template <int NR>
-__device__ __forceinline__ void half_compute_store(const StepParams &p,
-                                                   size_t idx0,
-                                                   const HalfLoads<NR> &L,
-                                                   uint32_t &fl)
+__device__ __forceinline__ void half_compute(const StepParams &p, size_t idx0,
+                                             const HalfLoads<NR> &L,
+                                             uint32_t &fl, uint4 (&out)[7])
 {
     uint32_t u[8];
     halves8(L.g[0], u);
@@ -307,47 +348,33 @@ __device__ __forceinline__ void half_compute_store(const StepParams &p,
     unpack8(L.v0, L.v1, v);
     unpack8(L.c0, L.c1, c);
 
-    uint32_t skipped = 0;
     uint32_t wbits[8];
-#pragma unroll
-    for(int e = 0; e < 8; e++) {
-        if(classify_half(u[e], fl)) {
-            skipped |= 1u << e;
-            wbits[e] = 0;
-        } else {
-            const float dw = __fmul_rn(half_bits_to_float(u[e]), p.alpha);
-            adam_element<true>(dw, m[e], v[e], c[e], p.b1t, p.b2t, p.lr, p.l2);
-            wbits[e] = float_to_half_bits(c[e]);
-        }
-    }
-    if(skipped) {
-        // a skipped element keeps its fp16 weight: fetch what the owner holds
-        const uint16_t *wold = p.h.W[p.rank] + idx0;
-#pragma unroll
-        for(int e = 0; e < 8; e++)
-            if(skipped & (1u << e))
-                wbits[e] = wold[e];
-    }
+    half_update<8>(p, u, m, v, c, wbits, p.h.W[p.rank] + idx0, fl);
+    pack8(m, out[0], out[1]);
+    pack8(v, out[2], out[3]);
+    pack8(c, out[4], out[5]);
+    out[6] = make_uint4(wbits[0] | (wbits[1] << 16), wbits[2] | (wbits[3] << 16),
+                        wbits[4] | (wbits[5] << 16), wbits[6] | (wbits[7] << 16));
+}
 
+template <int NR>
+__device__ __forceinline__ void half_compute_store(const StepParams &p,
+                                                   size_t idx0,
+                                                   const HalfLoads<NR> &L,
+                                                   uint32_t &fl)
+{
+    uint4 out[7];
+    half_compute<NR>(p, idx0, L, fl, out);
     const size_t li = idx0 - p.h.A;
-    uint4 a, b;
-    pack8(m, a, b);
-    st_stream(p.h.m + li, a);
-    st_stream(p.h.m + li + 4, b);
-    pack8(v, a, b);
-    st_stream(p.h.v + li, a);
-    st_stream(p.h.v + li + 4, b);
-    pack8(c, a, b);
-    st_stream(p.h.c + li, a);
-    st_stream(p.h.c + li + 4, b);
-
-    const uint4 wv = make_uint4(wbits[0] | (wbits[1] << 16),
-                                wbits[2] | (wbits[3] << 16),
-                                wbits[4] | (wbits[5] << 16),
-                                wbits[6] | (wbits[7] << 16));
+    st_stream(p.h.m + li, out[0]);
+    st_stream(p.h.m + li + 4, out[1]);
+    st_stream(p.h.v + li, out[2]);
+    st_stream(p.h.v + li + 4, out[3]);
+    st_stream(p.h.c + li, out[4]);
+    st_stream(p.h.c + li + 4, out[5]);
 #pragma unroll
     for(int q = 0; q < NR; q++)
-        *reinterpret_cast<uint4 *>(p.h.W[q] + idx0) = wv;
+        *reinterpret_cast<uint4 *>(p.h.W[q] + idx0) = out[6];
 }
 
 // Element-wise path for the (at most two) groups that straddle a shard edge,
@@ -490,89 +517,70 @@ __device__ __noinline__ uint32_t float_scalar(const StepParams &p, size_t idx0)
     return fl;
 }
 
-// ------------------------------------------------------------- the step kernel
+// ------------------------------------------------- step prologue and epilogue
 
-// UNR groups per thread are loaded before any is computed, to keep enough
-// bytes in flight per SM.
-template <int NR, int UNR, int MINB>
-__global__ void __launch_bounds__(kThreads, MINB)
-    fused_step_kernel(const __grid_constant__ StepParams p)
+// (N > 1) Announces "my gradients are final" to every rank and waits, bounded,
+// for every rank's announcement of the same step.  Returns non-zero in every
+// thread of the CTA when a wait ran out.
+template <int NR>
+__device__ __forceinline__ int step_begin(const StepParams &p)
 {
-    __shared__ int s_flag;
+    if(NR == 1 || !p.barrier)
+        return 0;
     const int tid = threadIdx.x;
     Ctrl *const my = p.ctrl[p.rank];
-    int aborted = 0;
-
-    if(NR > 1 && p.barrier) {
-        // "my gradients are final": one CTA tells every peer (and itself)
-        if(blockIdx.x == 0 && tid < NR)
-            st_release_sys(&p.ctrl[tid]->ready[p.rank], p.epoch);
-        int bad = 0;
-        if(tid < NR) {
-            if(!wait_epoch(&my->ready[tid], p.epoch, p.timeout_ns)) {
-                bad = 1;
-                if(atomicCAS(&my->status, 0u, (uint32_t)(-B200OPT_ETIMEOUT)) ==
-                       0u &&
-                   p.host) {
-                    p.host->where = 1;
-                    p.host->peer = tid;
-                }
-            }
-        }
-        aborted = __syncthreads_or(bad);
-    }
-
-    uint32_t fl = 0;
-    if(!aborted) {
-        const size_t stride = (size_t)gridDim.x * kThreads * UNR;
-        // fp16 group
-        {
-            const size_t ng = p.h.ngroups;
-            const size_t lo = p.h.o, hi = p.h.o + p.h.s;
-            for(size_t base = (size_t)blockIdx.x * kThreads * UNR; base < ng;
-                base += stride) {
-                HalfLoads<NR> L[UNR];
-                bool full[UNR];
-#pragma unroll
-                for(int k = 0; k < UNR; k++) {
-                    const size_t gid = base + (size_t)k * kThreads + tid;
-                    const size_t idx0 = p.h.A + gid * kVec;
-                    full[k] = gid < ng && idx0 >= lo && idx0 + kVec <= hi &&
-                              !p.force_scalar;
-                    if(full[k])
-                        half_load<NR>(p, idx0, L[k]);
-                }
-#pragma unroll
-                for(int k = 0; k < UNR; k++) {
-                    const size_t gid = base + (size_t)k * kThreads + tid;
-                    const size_t idx0 = p.h.A + gid * kVec;
-                    if(full[k])
-                        half_compute_store<NR>(p, idx0, L[k], fl);
-                    else if(gid < ng)
-                        fl |= half_scalar<NR>(p, idx0);
-                }
-            }
-        }
-        // fp32 group
-        {
-            const size_t ng = p.f.ngroups;
-            const size_t lo = p.f.o, hi = p.f.o + p.f.s;
-            for(size_t base = (size_t)blockIdx.x * kThreads; base < ng;
-                base += (size_t)gridDim.x * kThreads) {
-                const size_t gid = base + tid;
-                const size_t idx0 = p.f.A + gid * kVec;
-                if(gid < ng) {
-                    if(idx0 >= lo && idx0 + kVec <= hi && !p.force_scalar) {
-                        FloatLoads<NR> L;
-                        float_load<NR>(p, idx0, L);
-                        float_compute_store<NR>(p, idx0, L, fl);
-                    } else {
-                        fl |= float_scalar<NR>(p, idx0);
-                    }
-                }
+    if(blockIdx.x == 0 && tid < NR)
+        st_release_sys(&p.ctrl[tid]->ready[p.rank], p.epoch);
+    int bad = 0;
+    if(tid < NR) {
+        if(!wait_epoch(&my->ready[tid], p.epoch, p.timeout_ns)) {
+            bad = 1;
+            if(atomicCAS(&my->status, 0u, (uint32_t)(-B200OPT_ETIMEOUT)) == 0u &&
+               p.host) {
+                p.host->where = 1;
+                p.host->peer = tid;
             }
         }
     }
+    return __syncthreads_or(bad);
+}
+
+// The fp32 group (BatchNorm scales and biases in an fp16 network: a few tens
+// of thousands of elements) always takes the direct-load path.
+template <int NR>
+__device__ __forceinline__ void float_group_pass(const StepParams &p,
+                                                 uint32_t &fl)
+{
+    const int tid = threadIdx.x;
+    const size_t ng = p.f.ngroups;
+    const size_t lo = p.f.o, hi = p.f.o + p.f.s;
+    for(size_t base = (size_t)blockIdx.x * blockDim.x; base < ng;
+        base += (size_t)gridDim.x * blockDim.x) {
+        const size_t gid = base + tid;
+        const size_t idx0 = p.f.A + gid * kVec;
+        if(gid < ng) {
+            if(idx0 >= lo && idx0 + kVec <= hi && !p.force_scalar) {
+                FloatLoads<NR> L;
+                float_load<NR>(p, idx0, L);
+                float_compute_store<NR>(p, idx0, L, fl);
+            } else {
+                fl |= float_scalar<NR>(p, idx0);
+            }
+        }
+    }
+}
+
+// Folds the per-thread flag bits into one word per rank and, in the last CTA
+// of the launch to get here, finishes the step: publishes this rank's flag
+// word to all ranks, waits (bounded) until every rank has finished reading
+// gradients and writing weights, and leaves the flag sums in pinned host
+// memory.  `s_flag` is one int of shared memory.
+template <int NR>
+__device__ __forceinline__ void step_finish(const StepParams &p, uint32_t fl,
+                                            int *s_flag)
+{
+    const int tid = threadIdx.x;
+    Ctrl *const my = p.ctrl[p.rank];
 
     // one flag word per warp, then at most one atomic per warp that saw any
     fl = __reduce_or_sync(0xffffffffu, fl);
@@ -593,16 +601,16 @@ __global__ void __launch_bounds__(kThreads, MINB)
     if((tid & 31) == 0 && fl)
         atomicOr(&my->local_flags, fl);
 
-    // completion: the last CTA of this launch finishes the step
+    // the last CTA of this launch finishes the step
     if(NR > 1)
         __threadfence_system();  // weight stores into peers before the signal
     else
         __threadfence();
     __syncthreads();
     if(tid == 0)
-        s_flag = atomicAdd(&my->cta_done, 1u) == gridDim.x - 1;
+        *s_flag = atomicAdd(&my->cta_done, 1u) == gridDim.x - 1;
     __syncthreads();
-    if(!s_flag)
+    if(!*s_flag)
         return;
     __threadfence();
 
@@ -664,6 +672,49 @@ __global__ void __launch_bounds__(kThreads, MINB)
         my->cta_done = 0;
         __threadfence_system();
     }
+}
+
+// ------------------------------------------------ step kernel, direct loads
+
+// Every thread loads its 8-element groups straight into registers (UNR groups
+// before any is computed, to keep enough bytes in flight per SM).
+template <int NR, int UNR, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB)
+    fused_step_kernel(const __grid_constant__ StepParams p)
+{
+    __shared__ int s_flag;
+    const int tid = threadIdx.x;
+    uint32_t fl = 0;
+    if(!step_begin<NR>(p)) {
+        const size_t stride = (size_t)gridDim.x * kThreads * UNR;
+        const size_t ng = p.h.ngroups;
+        const size_t lo = p.h.o, hi = p.h.o + p.h.s;
+        for(size_t base = (size_t)blockIdx.x * kThreads * UNR; base < ng;
+            base += stride) {
+            HalfLoads<NR> L[UNR];
+            bool full[UNR];
+#pragma unroll
+            for(int k = 0; k < UNR; k++) {
+                const size_t gid = base + (size_t)k * kThreads + tid;
+                const size_t idx0 = p.h.A + gid * kVec;
+                full[k] = gid < ng && idx0 >= lo && idx0 + kVec <= hi &&
+                          !p.force_scalar;
+                if(full[k])
+                    half_load<NR>(p, idx0, L[k]);
+            }
+#pragma unroll
+            for(int k = 0; k < UNR; k++) {
+                const size_t gid = base + (size_t)k * kThreads + tid;
+                const size_t idx0 = p.h.A + gid * kVec;
+                if(full[k])
+                    half_compute_store<NR>(p, idx0, L[k], fl);
+                else if(gid < ng)
+                    fl |= half_scalar<NR>(p, idx0);
+            }
+        }
+        float_group_pass<NR>(p, fl);
+    }
+    step_finish<NR>(p, fl, &s_flag);
 }
 
 // master := float(fp16 weights) over the shard (AdamMixed constructor,

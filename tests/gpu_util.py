@@ -24,7 +24,7 @@ def stream_ptr(device=0):
 class Program:
     """N ranks of the CUDA path with the weights/gradients API the tests need."""
 
-    def __init__(self, nranks, n_half, n_float=0, devices=None):
+    def __init__(self, nranks, n_half, n_float=0, devices=None, variant=None):
         devices = devices or [0] * nranks
         self.N = nranks
         self.devices = devices
@@ -32,6 +32,8 @@ class Program:
                        else [AdamGroup.create(0, 1, devices[0], n_half, n_float)])
         self.Wh, self.Gh, self.Wf, self.Gf = [], [], [], []
         for g in self.groups:
+            if variant is not None:
+                g.set_option(capi.OPT_KERNEL_VARIANT, variant)
             w, gr = g.buffers(capi.HALF)
             self.Wh.append(w)
             self.Gh.append(gr)

@@ -163,11 +163,14 @@ def test_seam_reproduces_golden_fixtures(path):
 
 # ------------------------------------------------------------- handle API, 1 rank
 
+VARIANTS = [1, 6, 2, 3, 4, 5]  # direct loads (x2), bulk-copy staging (x4)
+
+
 def _run_trajectory(oracle, nranks, n_half, n_float, steps, lr, l2, scale0, seed,
-                    inject_every=0, check_every=1, tol_final=TOL_100):
+                    inject_every=0, check_every=1, tol_final=TOL_100, variant=None):
     W0 = synth.weights_half(n_half, seed=seed) if n_half else None
     Wf0 = synth.weights_float(n_float, seed=seed) if n_float else None
-    prog = Program(nranks, n_half, n_float)
+    prog = Program(nranks, n_half, n_float, variant=variant)
     prog.set_weights([W0] * nranks if n_half else None, [Wf0] * nranks if n_float else None)
     ost = oracle.MultiRankState(nranks, [W0] * nranks if n_half else None,
                                 [Wf0] * nranks if n_float else None)
@@ -218,15 +221,19 @@ def _run_trajectory(oracle, nranks, n_half, n_float, steps, lr, l2, scale0, seed
         prog.close()
 
 
-def test_single_rank_100_steps_config2_distribution(oracle):
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_single_rank_100_steps_config2_distribution(oracle, variant):
     """n = 2^20, 100 steps, gradients N(0,1e-3)*scale, an inf every 50th step."""
     _run_trajectory(oracle, 1, 1 << 20, 0, 100, 1e-3, 0.01, 1024.0, seed=41,
-                    inject_every=50, check_every=25)
+                    inject_every=50, check_every=25, variant=variant)
 
 
-def test_single_rank_both_groups_small(oracle):
-    for n_half, n_float in ((16, 16), (272, 48), (4112, 1040), (0, 528), (100000 - 16, 0)):
-        _run_trajectory(oracle, 1, n_half, n_float, 6, 1e-2, 0.01, 64.0, seed=42, inject_every=4)
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_single_rank_both_groups_small(oracle, variant):
+    for n_half, n_float in ((16, 16), (272, 48), (4112, 1040), (0, 528), (100000 - 16, 0),
+                            (5, 3), (2048 * 9 + 8, 0)):
+        _run_trajectory(oracle, 1, n_half, n_float, 6, 1e-2, 0.01, 64.0, seed=42, inject_every=4,
+                        variant=variant)
 
 
 def test_iteration_counter_advances_on_overflow_steps(oracle):
@@ -328,21 +335,24 @@ def test_export_import_state_resumes_exactly(oracle):
 
 # ------------------------------------------- several ranks on one GPU (serial mode)
 
-@pytest.mark.parametrize("nranks", [2, 3, 4, 8])
-def test_multirank_serial_matches_oracle(oracle, nranks):
+@pytest.mark.parametrize("variant", [1, 2, 3, 4, 5])
+@pytest.mark.parametrize("nranks", [2, 3, 4, 5, 6, 7, 8])
+def test_multirank_serial_matches_oracle(oracle, nranks, variant):
     # sizes chosen to hit: shard edges off the 8-element grid (16/8 = 2 per rank),
-    # a tail nobody owns (n % nranks != 0), and a size with full vector groups
-    for n_half, n_float in ((16, 16), (272, 48), (8208, 528)):
+    # a tail nobody owns (n % nranks != 0), sizes with full vector groups, and
+    # shards of several 2048-element tiles with a ragged last tile
+    for n_half, n_float in ((16, 16), (272, 48), (8208, 528), (2048 * 3 * nranks + 80, 0)):
         _run_trajectory(oracle, nranks, n_half, n_float, 5, 1e-2, 0.01, 64.0, seed=50 + nranks,
-                        inject_every=3)
+                        inject_every=3, variant=variant)
 
 
+@pytest.mark.parametrize("variant", [1, 4])
 @pytest.mark.parametrize("nranks", [2, 4, 8])
-def test_special_values_at_shard_edges(oracle, nranks):
+def test_special_values_at_shard_edges(oracle, nranks, variant):
     n = 64 * nranks
     s = n // nranks
     W0 = synth.weights_half(n, seed=60)
-    prog = Program(nranks, n)
+    prog = Program(nranks, n, variant=variant)
     ost = oracle.MultiRankState(nranks, [W0] * nranks)
     try:
         prog.set_weights([W0] * nranks)
