@@ -51,5 +51,27 @@ def build_library(force=False, verbose=False):
     return LIB
 
 
+DRIVER = os.path.join(HERE, "host", "mt_driver")
+
+
+def build_driver(force=False):
+    """Compiles host/mt_driver (Saga's one-thread-per-GPU model over the C ABI)."""
+    src = os.path.join(HERE, "host", "mt_driver.cpp")
+    hdr = os.path.join(HERE, "host", "b200_adam_op.hpp")
+    build_library()
+    if not force and os.path.exists(DRIVER) and all(
+            os.path.getmtime(DRIVER) > os.path.getmtime(f) for f in (src, hdr, LIB)):
+        return DRIVER
+    cmd = [_nvcc(), "-std=c++17", "-O2", "-x", "cu", src, "-o", DRIVER,
+           "-I", os.path.join(HERE, "..", "include"), "-I", os.path.join(HERE, "host"),
+           "-L", HERE, "-lb200opt", "-Xlinker", "-rpath," + "$ORIGIN/..", "-lpthread"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("nvcc failed building mt_driver")
+    return DRIVER
+
+
 if __name__ == "__main__":
     print(build_library(force=True, verbose="-v" in sys.argv))
+    print(build_driver(force=True))

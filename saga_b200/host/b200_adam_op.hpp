@@ -1,0 +1,139 @@
+// -*-c++-*-
+//
+// Host-side shim that puts the b200opt C ABI behind Saga's optimizer op
+// interface.  It is meant to be compiled INSIDE the Saga tree, included from
+// src/cuda/cuda_optimizer.cpp after that file's own includes ("saga.hpp",
+// "cuda_common.hpp", "cuda_tensor.hpp"), with -DHAVE_B200OPT and this
+// repository's include/ directory on the include path; see INTEGRATION.md for
+// the patch that uses it.
+//
+// What it mirrors (paths relative to the Saga project root):
+//   struct Optimizer / AdamF32 / AdamMixed   src/cuda/cuda_optimizer.cpp:37-194
+//       -> B200Adam: one CudaOperation that runs BOTH dtype groups in one
+//          fused kernel launch (reduce-scatter + Adam + all-gather + flag sum)
+//   CudaProgram::create_optimizers           src/cuda/cuda_optimizer.cpp:276-292
+//       -> b200_create_optimizers(): same flat layout (16-element padding, FLOAT
+//          group and HALF group), tensors re-pointed into library-owned memory
+//   ncclCommInitAll                          src/cuda/cuda_common.cpp:116-127
+//       -> B200Rendezvous: the per-engine meeting point where the rank threads
+//          exchange their handles (one std::thread per GPU, as in Saga)
+//   flag block of CudaProgram::step          src/cuda/cuda_program.cpp:282-307
+//       -> B200Adam::finish_step(): stream sync + flag sums + scale policy
+//
+// Error convention: the C ABI returns status codes; the shim turns a non-zero
+// status into std::runtime_error so that CudaProgram::runOps reports it the
+// way it reports any failing op (src/cuda/cuda_program.cpp:226-231).
+#pragma once
+
+#include <condition_variable>
+#include <map>
+#include <mutex>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "b200opt.h"
+
+namespace saga {
+
+// Meeting point of the rank threads of one engine.  Every rank creates its own
+// handle on its own device, then joins; join() returns when all ranks have
+// joined and this rank has attached every peer.
+class B200Rendezvous {
+public:
+    explicit B200Rendezvous(int nranks) : m_handles(nranks, nullptr) {}
+
+    void join(int rank, b200opt_t *h)
+    {
+        const int n = (int)m_handles.size();
+        {
+            std::unique_lock<std::mutex> lock(m_mutex);
+            m_handles[rank] = h;
+            m_joined++;
+            m_cond.notify_all();
+            m_cond.wait(lock, [&] { return m_joined >= n; });
+        }
+        for(int q = 0; q < n; q++) {
+            if(q == rank)
+                continue;
+            const int rc = b200opt_attach_local(h, q, m_handles[q]);
+            if(rc != B200OPT_OK)
+                throw std::runtime_error(std::string("b200opt_attach_local: ") +
+                                         b200opt_last_error(h));
+        }
+        // nobody may step before every rank has wired its peers
+        std::unique_lock<std::mutex> lock(m_mutex);
+        m_wired++;
+        m_cond.notify_all();
+        m_cond.wait(lock, [&] { return m_wired >= n; });
+    }
+
+private:
+    std::mutex m_mutex;
+    std::condition_variable m_cond;
+    std::vector<b200opt_t *> m_handles;
+    int m_joined = 0;
+    int m_wired = 0;
+};
+
+#ifdef HAVE_B200OPT  // the part below needs Saga's own headers
+
+// Non-owning view of library memory, so that tensor storages can alias it the
+// way they alias the reference's flat allocation
+// (src/cuda/cuda_optimizer.cpp:245-249).  Needs the one-line constructor
+// `CudaTensorStorageMemory(void *external)` that INTEGRATION.md adds.
+
+struct B200Adam : public CudaOperation {
+    B200Adam(CudaProgram &p, b200opt_t *handle, const CudaOpArgs &inputs,
+             const CudaOpArgs &outputs)
+      : CudaOperation("b200-adam")
+      , m_handle(handle)
+      , m_inputs(inputs)
+      , m_outputs(outputs)
+      , m_ctx(p.m_ctx)
+    {
+    }
+
+    ~B200Adam() { b200opt_destroy(m_handle); }
+
+    // AdamF32::exec + AdamMixed::exec (src/cuda/cuda_optimizer.cpp:76-113,
+    // 148-186): iteration counter, bias corrections, 1/scale, reduce-scatter,
+    // update, all-gather -- all inside b200opt_step.  Asynchronous.
+    void exec(CudaProgram &p) override
+    {
+        const int rc = b200opt_step(m_handle, p.m_pc.learning_rate,
+                                    p.m_pc.l2_lambda, p.m_mp_scaling,
+                                    p.m_ctx->m_stream);
+        if(rc != B200OPT_OK)
+            throw std::runtime_error(std::string("b200opt_step: ") +
+                                     b200opt_last_error(m_handle));
+    }
+
+    // Replaces the flag block at the end of CudaProgram::step
+    // (src/cuda/cuda_program.cpp:282-307): the cross-rank flag sum has already
+    // happened inside the step kernel; this waits for the stream, reads the
+    // sums and applies the reference's scale policy.
+    void finish_step(CudaProgram &p)
+    {
+        uint32_t flags[3];
+        const int rc = b200opt_flags(m_handle, p.m_ctx->m_stream, flags);
+        if(rc != B200OPT_OK)
+            throw std::runtime_error(std::string("b200opt_flags: ") +
+                                     b200opt_last_error(m_handle));
+        if(p.m_mp_enabled)
+            b200opt_policy_update(&p.m_mp_scaling, flags,
+                                  B200OPT_POLICY_REFERENCE, nullptr, 0);
+    }
+
+    CudaOpArgs listInputs() const override { return m_inputs; }
+    CudaOpArgs listOutputs() const override { return m_outputs; }
+
+    b200opt_t *m_handle;
+    CudaOpArgs m_inputs;
+    CudaOpArgs m_outputs;
+    const std::shared_ptr<CudaContext> m_ctx;
+};
+
+#endif  // HAVE_B200OPT
+
+}  // namespace saga
