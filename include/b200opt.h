@@ -42,6 +42,7 @@ extern "C" {
 #define B200OPT_ETIMEOUT (-4)     /* a peer rank did not arrive within the wait limit */
 #define B200OPT_ESTATE (-5)       /* call not valid in the handle's state (peers not wired, ...) */
 #define B200OPT_EUNSUPPORTED (-6) /* built without the needed support (e.g. NCCL) */
+#define B200OPT_ETOOBIG (-7)      /* size beyond what the fixed scratch of an entry point covers */
 
 /* dtype groups, the two the reference builds optimizers for
  * (src/cuda/cuda_optimizer.cpp:276-292) */
@@ -241,6 +242,44 @@ B200OPT_API int b200opt_adam_float(size_t n, float *weights, const float *gradie
                        float *mvec, float *vvec, float b1t, float b2t,
                        float learning_rate, float l2_lambda, uint32_t *aux,
                        void *stream);
+
+/*
+ * No counterpart in the reference: the same one-GPU mixed-precision Adam step
+ * as b200opt_adam_mixed for callers that must not allocate device memory.
+ *
+ * Who that is: a program whose device memory is planned once up front (Saga
+ * itself lays every tensor out in one arena before the first step and never
+ * allocates again), a step loop that cannot tolerate the device-wide
+ * synchronisation an allocation or free may imply, or an embedder running under
+ * a fixed memory reservation.  The handle API above needs cudaMalloc for its
+ * control block; this entry point needs none.  The kernel's scratch (the
+ * counter and flag words its CTAs meet on) lives in a fixed
+ * B200OPT_STATIC_SCRATCH_BYTES array inside the library image, which every GPU
+ * that loads the library holds until the process exits.  Nothing in this call
+ * allocates or frees memory, on the device or through any library.
+ *
+ *   - Inputs and outputs are the caller's: weights/gradients (fp16), mvec, vvec,
+ *     cvec (fp32), all n elements and 16-byte aligned, and flags_out, three
+ *     u32 in device memory which receive {range, inf, nan} as 0 or 1
+ *     (overwritten, not accumulated).
+ *   - n may not exceed B200OPT_STATIC_MAX_ELEMS; larger sizes return
+ *     B200OPT_ETOOBIG and launch nothing.
+ *   - The first call on a device looks up the array's device address; make that
+ *     first call during start-up, before any stream capture is open.
+ *   - All calls on one GPU share the array and it keeps what the last call left:
+ *     each call clears the words that must start at zero on `stream` before its
+ *     kernel.  Two calls that overlap on the same GPU (different streams, or
+ *     different host threads) race on it and give undefined flags; serialise
+ *     them on one stream.
+ */
+#define B200OPT_STATIC_SCRATCH_BYTES 4096
+#define B200OPT_STATIC_MAX_ELEMS ((size_t)1 << 30)
+B200OPT_API int b200opt_adam_mixed_static(size_t n, float alpha, void *weights,
+                                          const void *gradients, float *mvec,
+                                          float *vvec, float *cvec, float b1t,
+                                          float b2t, float learning_rate,
+                                          float l2_lambda, uint32_t *flags_out,
+                                          void *stream);
 
 /* ------------------------------------------------------- state and options */
 

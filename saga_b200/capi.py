@@ -9,7 +9,8 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200opt.so")
 
-OK, EINVAL, ECUDA, ENOMEM, ETIMEOUT, ESTATE, EUNSUPPORTED = 0, -1, -2, -3, -4, -5, -6
+OK, EINVAL, ECUDA, ENOMEM, ETIMEOUT, ESTATE, EUNSUPPORTED, ETOOBIG = 0, -1, -2, -3, -4, -5, -6, -7
+STATIC_MAX_ELEMS = 1 << 30
 HALF, FLOAT = 0, 1
 POLICY_REFERENCE, POLICY_INTERVAL = 0, 1
 PATH_AUTO, PATH_PEER, PATH_NCCL = 0, 1, 2
@@ -46,6 +47,7 @@ SIGNATURES = {
     "b200opt_bias_corrections": (_i, [_i, _fp, _fp]),
     "b200opt_adam_mixed": (_i, [_sz, _f, _vp, _vp, _vp, _vp, _vp, _f, _f, _f, _f, _vp, _vp]),
     "b200opt_adam_float": (_i, [_sz, _vp, _vp, _vp, _vp, _f, _f, _f, _f, _vp, _vp]),
+    "b200opt_adam_mixed_static": (_i, [_sz, _f, _vp, _vp, _vp, _vp, _vp, _f, _f, _f, _f, _vp, _vp]),
     "b200opt_get_iter": (_i, [_vp, C.POINTER(_i)]),
     "b200opt_set_iter": (_i, [_vp, _i]),
     "b200opt_export_state": (_i, [_vp, _i, _i, _vp, _sz, C.POINTER(_sz)]),

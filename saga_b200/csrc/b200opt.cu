@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <string>
 
@@ -283,6 +284,8 @@ const char *b200opt_strerror(int status)
     case B200OPT_ETIMEOUT: return "a peer rank did not arrive in time";
     case B200OPT_ESTATE: return "call not valid in this state";
     case B200OPT_EUNSUPPORTED: return "not supported by this build";
+    case B200OPT_ETOOBIG:
+        return "size exceeds what this entry point's fixed scratch covers";
     }
     return "unknown status";
 }
@@ -795,6 +798,87 @@ int b200opt_adam_float(size_t n, float *weights, const float *gradients,
     p.force_scalar = !(aligned16(weights) && aligned16(gradients) &&
                        aligned16(mvec) && aligned16(vvec));
     return launch_step(p, 1, sms, seam_tuning(), (cudaStream_t)stream) == cudaSuccess
+               ? B200OPT_OK
+               : B200OPT_ECUDA;
+}
+
+// ---------------------------------------------------------------------------
+// Entry point for callers that must not allocate: its scratch is this array.
+// In host code the array's name stands for the symbol, not for a device
+// address; the address a kernel can use comes from cudaGetSymbolAddress, asked
+// once per device with that device current.
+static __device__ __align__(256) unsigned char
+    g_static_scratch[B200OPT_STATIC_SCRATCH_BYTES];
+static_assert(sizeof(Ctrl) <= B200OPT_STATIC_SCRATCH_BYTES,
+              "the control block must fit the static scratch");
+
+static int static_scratch_address(Ctrl **out)
+{
+    static std::mutex mu;
+    static void *per_device[64] = {};
+    int dev = 0;
+    if(cudaGetDevice(&dev) != cudaSuccess)
+        return B200OPT_ECUDA;
+    if(dev < 0 || dev >= 64)
+        return B200OPT_EUNSUPPORTED;
+    std::lock_guard<std::mutex> lock(mu);
+    if(!per_device[dev]) {
+        void *ptr = nullptr;
+        if(cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            return B200OPT_ECUDA;
+        }
+        per_device[dev] = ptr;
+    }
+    *out = static_cast<Ctrl *>(per_device[dev]);
+    return B200OPT_OK;
+}
+
+int b200opt_adam_mixed_static(size_t n, float alpha, void *weights,
+                              const void *gradients, float *mvec, float *vvec,
+                              float *cvec, float b1t, float b2t,
+                              float learning_rate, float l2_lambda,
+                              uint32_t *flags_out, void *stream)
+{
+    if(n > B200OPT_STATIC_MAX_ELEMS)
+        return B200OPT_ETOOBIG;
+    if(!flags_out ||
+       (n && (!weights || !gradients || !mvec || !vvec || !cvec)))
+        return B200OPT_EINVAL;
+    if(!(aligned16(weights) && aligned16(gradients) && aligned16(mvec) &&
+         aligned16(vvec) && aligned16(cvec)))
+        return B200OPT_EINVAL;
+    Ctrl *ctrl = nullptr;
+    int rc = static_scratch_address(&ctrl);
+    if(rc)
+        return rc;
+    int dev = 0, sms = 0;
+    if(cudaGetDevice(&dev) != cudaSuccess ||
+       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) !=
+           cudaSuccess)
+        return B200OPT_ECUDA;
+    cudaStream_t st = (cudaStream_t)stream;
+    // the shared array keeps the last call's contents: start from zero
+    if(cudaMemsetAsync(ctrl, 0, sizeof(Ctrl), st) != cudaSuccess)
+        return B200OPT_ECUDA;
+    StepParams p;
+    memset(&p, 0, sizeof(p));
+    p.h.W[0] = (uint16_t *)weights;
+    p.h.G[0] = (const uint16_t *)gradients;
+    p.h.m = mvec;
+    p.h.v = vvec;
+    p.h.c = cvec;
+    p.h.s = n;
+    p.h.ngroups = (n + kVec - 1) / kVec;
+    p.alpha = alpha;
+    p.b1t = b1t;
+    p.b2t = b2t;
+    p.lr = learning_rate;
+    p.l2 = l2_lambda;
+    p.timeout_ns = 10000000000ull;
+    p.ctrl[0] = ctrl;        // the fixed array, not an allocation
+    p.flags_dev = flags_out;  // written by the last CTA, also when n == 0
+    return launch_step(p, 1, sms, seam_tuning(), st) == cudaSuccess
                ? B200OPT_OK
                : B200OPT_ECUDA;
 }
