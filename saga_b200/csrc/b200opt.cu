@@ -21,6 +21,12 @@ using namespace b200;
 namespace {
 
 constexpr size_t kCtrlBytes = 4096;
+// Shard state is padded so that element i of the flat buffer sits at [i - A]
+// with A = the shard start rounded down to this many elements: every array
+// (gradients, weights, m, v, master) then has the same phase relative to the
+// tiles of the step kernels, and interior tiles start on 2 KB / 4 KB boundaries
+// whatever the reference's shard boundary r*(n/N) happens to be.
+constexpr size_t kStateAlign = 4096;
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block must fit its page");
 
 inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -318,10 +324,10 @@ int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
     // (src/cuda/cuda_optimizer.cpp:85-86,157-158 of the Saga tree)
     h->sh = n_half / nranks;
     h->oh = h->sh * rank;
-    h->Ah = h->oh & ~(size_t)(kVec - 1);
+    h->Ah = h->oh & ~(size_t)(kStateAlign - 1);
     h->sf = n_float / nranks;
     h->of = h->sf * rank;
-    h->Af = h->of & ~(size_t)(kVec - 1);
+    h->Af = h->of & ~(size_t)(kStateAlign - 1);
 
     h->off_wh = kCtrlBytes;
     h->off_gh = h->off_wh + round_up(n_half * 2, 256);
@@ -351,9 +357,7 @@ int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
             rc = B200OPT_ECUDA;
             break;
         }
-        // shard state, padded so that element i of the flat buffer sits at
-        // [i - A]: the vector path then sees the same 8-element phase in every
-        // array
+        // shard state, padded so that element i of the flat buffer sits at [i - A]
         h->state_h_elems = h->sh ? round_up(h->oh + h->sh - h->Ah, kVec) : 0;
         h->state_f_elems = h->sf ? round_up(h->of + h->sf - h->Af, kVec) : 0;
         // one allocation for all shard state: [m | v | master | m32 | v32]

@@ -240,22 +240,30 @@ __global__ void __launch_bounds__(THREADS)
         const size_t lo = p.h.o, hi = p.h.o + p.h.s;
         const size_t F0 = (lo + kVec - 1) & ~(size_t)(kVec - 1);
         const size_t F1 = hi & ~(size_t)(kVec - 1);
-        const size_t nfull = (p.h.s && F1 > F0) ? F1 - F0 : 0;
-        const size_t ntiles = (nfull + TILE - 1) / TILE;
+        const bool any_full = p.h.s && F1 > F0;
+        // Tiles are cut on multiples of TILE of the flat buffer's index, so that
+        // all but the first and last tile of a shard start on a 2 KB boundary of
+        // the fp16 arrays (4 KB of the fp32 arrays) whatever the shard's offset.
+        const size_t t_first = F0 / TILE;
+        const size_t ntiles = any_full ? (F1 - 1) / TILE - t_first + 1 : 0;
         const size_t nmine =
             ntiles > blockIdx.x
                 ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x
                 : 0;
 
+        auto tile_start = [&](size_t k) -> size_t {
+            const size_t t = t_first + blockIdx.x + k * gridDim.x;
+            const size_t b = t * TILE;
+            return b > F0 ? b : F0;
+        };
         auto tile_elems = [&](size_t k) -> uint32_t {
-            const size_t t = blockIdx.x + k * gridDim.x;
-            const size_t left = nfull - t * TILE;
-            return (uint32_t)(left < (size_t)TILE ? left : (size_t)TILE);
+            const size_t t = t_first + blockIdx.x + k * gridDim.x;
+            const size_t e = (t + 1) * TILE;
+            return (uint32_t)((e < F1 ? e : F1) - tile_start(k));
         };
         auto issue_loads = [&](size_t k) {
             const int s = (int)(k % STAGES);
-            const size_t t = blockIdx.x + k * gridDim.x;
-            const size_t e0 = F0 + t * TILE;    // global element index
+            const size_t e0 = tile_start(k);    // global element index
             const size_t l0 = e0 - p.h.A;       // index into the shard state
             const uint32_t te = tile_elems(k);
             unsigned char *st = stage_mem + (size_t)s * kStage;
@@ -289,8 +297,7 @@ __global__ void __launch_bounds__(THREADS)
                 break;
             }
             const uint32_t te = tile_elems(k);
-            const size_t t = blockIdx.x + k * gridDim.x;
-            const size_t e0 = F0 + t * TILE;
+            const size_t e0 = tile_start(k);
             if((uint32_t)tid * VEC < te) {
                 staged_update<NR, VEC, TILE>(p, st, tid, e0 + (size_t)tid * VEC,
                                              fl);
@@ -342,7 +349,7 @@ __global__ void __launch_bounds__(THREADS)
                 fl |= half_scalar<NR>(p, p.h.A + gid * kVec);
         } else if(blockIdx.x == 0 && p.h.s) {
             if(tid == 0 && lo != F0)
-                fl |= half_scalar<NR>(p, p.h.A);
+                fl |= half_scalar<NR>(p, lo & ~(size_t)(kVec - 1));
             if(tid == 1 && F1 < hi && F1 >= F0)
                 fl |= half_scalar<NR>(p, F1);
         }
