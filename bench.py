@@ -117,6 +117,7 @@ def cpu_baseline(n, budget_s=12.0, max_steps=5000):
     no CPU implementation of this path), all host threads, on the full buffer."""
     from oracle import oracle as orc
     from tests import synth
+    orc.use_all_host_threads()
     w = synth.weights_half(n, seed=1)
     c = orc.master_init(w)
     m = np.zeros(n, np.float32)
@@ -143,31 +144,43 @@ def cpu_baseline(n, budget_s=12.0, max_steps=5000):
 
 def run_reference_arm(args):
     """--impl reference: the reference has no CPU (or buildable dnnl) training
-    path, so this arm times the CPU restatement of its CUDA Adam kernel on the
-    host cores, one step = one pass over the same 25.6 M-parameter buffer."""
+    path, so this arm times the CPU restatement of its path on all host cores:
+    per step the rank-ordered sum of the N ranks' gradient buffers (N > 1) and
+    the mixed-precision Adam update of the same 25.6 M-parameter buffer."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from oracle import oracle as orc
     from tests import synth
+    cores = orc.use_all_host_threads()
+    world = max(args.gpus, 1)
     sizes, lay = workload()
     n = lay.total
     w = synth.weights_half(n, seed=1)
     c = orc.master_init(w)
     m = np.zeros(n, np.float32)
     v = np.zeros(n, np.float32)
-    g = synth.grads_half(n, SCALE0, 1, seed=1)
+    grads = [synth.grads_half(n, SCALE0, 1, rank=r, seed=1) for r in range(world)]
+    gsum = np.empty(n, np.uint16)
     al = orc.alpha(SCALE0)
     steps = min(args.steps, 200)
-    for it in range(1, args.warmup + 1):
+
+    def one_step(it):
         b1t, b2t = orc.bias_corrections(it)
+        g = orc.reduce_half_threads(grads, gsum) if world > 1 else grads[0]
         orc.adam_mixed(w, g, m, v, c, al, b1t, b2t, LR, L2, threads=True)
+
+    for it in range(1, args.warmup + 1):
+        one_step(it)
     t0 = time.perf_counter()
     for it in range(args.warmup + 1, args.warmup + steps + 1):
-        b1t, b2t = orc.bias_corrections(it)
-        orc.adam_mixed(w, g, m, v, c, al, b1t, b2t, LR, L2, threads=True)
+        one_step(it)
     dt = time.perf_counter() - t0
-    value = n * steps / dt
+    value = world * n * steps / dt
+    sample = (f"{steps} full steps over all {n} parameters"
+              + (f", each summing {world} gradient buffers first" if world > 1 else "")
+              + f" ({dt:.1f} s; CPU restatement of src/cuda adam_kernel_mp, OpenMP over elements; "
+                "the reference ships no CPU training path)")
     line = {
         "impl": "reference", "metric": "fused grad-reduce+Adam params/sec", "value": value,
         "unit": "params/s", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
@@ -175,11 +188,8 @@ def run_reference_arm(args):
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "config2: 25.6M fp16 params in 160 tensors, 1 optimizer step",
                    "n_params": n, "tensors": len(sizes)},
-        "cpu_baseline": {"value": value, "unit": "params/s", "cores": orc.num_threads(),
-                         "kind": "port",
-                         "sample": f"{steps} full steps of {n} parameters on the host cores "
-                                   "(CPU restatement of src/cuda adam_kernel_mp; the reference "
-                                   "ships no CPU training path)"},
+        "cpu_baseline": {"value": value, "unit": "params/s", "cores": cores, "kind": "port",
+                         "sample": sample},
         "e2e": {"value": value, "unit": "params/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
     }
@@ -236,15 +246,8 @@ def main():
 
     grp = AdamGroup.create(rank, world, local, n, 0)
     if world > 1:
-        def gather(b):
-            out = [None] * world
-            dist.all_gather_object(out, b)
-            return out
-        grp.attach_process_group(gather)
-        if args.path in ("auto", "nccl"):
-            uid = [AdamGroup.nccl_unique_id() if rank == 0 else None]
-            dist.broadcast_object_list(uid, src=0)
-            grp.nccl_init(uid[0])
+        from saga_b200 import launch
+        launch.wire_process_group(grp, with_nccl=True)
         grp.set_option(capi.OPT_PATH, {"auto": capi.PATH_AUTO, "peer": capi.PATH_PEER,
                                        "nccl": capi.PATH_NCCL}[args.path])
     if args.ctas_per_sm:
@@ -276,6 +279,16 @@ def main():
     sampler = ClockSampler(local) if rank == 0 else None
     scaler = LossScaler(SCALE0)
 
+    def timed_steps(k):
+        """k steps back to back on one stream; device time in ms (this rank)."""
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(k):
+            grp.exec(LR, L2, scaler.scale, sp)
+        b.record(stream)
+        torch.cuda.synchronize(dev)
+        return a.elapsed_time(b)
+
     # ---- device-resident throughput: K steps back to back on one stream
     for _ in range(args.warmup):
         grp.exec(LR, L2, scaler.scale, sp)
@@ -284,16 +297,59 @@ def main():
     launches0 = grp.launch_count
     if sampler:
         sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    for _ in range(args.steps):
-        grp.exec(LR, L2, scaler.scale, sp)
-    e1.record(stream)
-    torch.cuda.synchronize(dev)
+    ms = timed_steps(args.steps)
     barrier()
-    ms = e0.elapsed_time(e1)
     launches = grp.launch_count - launches0
     flags = grp.flags(sp)
+
+    # ---- N > 1: the reference's own sequence (ncclReduceScatter, Adam on the shard,
+    # ncclAllGather, 3-word all-reduce) on the same buffers, for comparison
+    nccl_ms = None
+    if world > 1 and args.path != "nccl":
+        grp.set_option(capi.OPT_PATH, capi.PATH_NCCL)
+        k = min(args.steps, 200)
+        for _ in range(5):
+            grp.exec(LR, L2, scaler.scale, sp)
+        grp.flags(sp)
+        barrier()
+        nccl_ms = timed_steps(k) / k
+        grp.flags(sp)
+        barrier()
+        grp.set_option(capi.OPT_PATH, {"auto": capi.PATH_AUTO, "peer": capi.PATH_PEER}[args.path])
+
+    # ---- N = 1: the reference's own kernel (src/cuda/cuda_kernels.cu compiled
+    # unmodified for sm_100a, oracle/_ref) on buffers of the same size
+    ref_gpu = None
+    if world == 1 and rank == 0:
+        from oracle import oracle as orc
+        if orc.ref_available():
+            R = orc.ref()
+            rw, rg = w.clone(), g.clone()
+            rm, rv = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+            rc_ = rw.float()
+            aux = torch.zeros(4, dtype=torch.int32, device=dev)
+            b1t, b2t = orc.bias_corrections(1)
+
+            def ref_step():
+                R.sagaref_adam_mixed(n, float(orc.alpha(SCALE0)), rw.data_ptr(), rg.data_ptr(),
+                                     rm.data_ptr(), rv.data_ptr(), rc_.data_ptr(), float(b1t),
+                                     float(b2t), LR, L2, aux.data_ptr(), sp)
+            for _ in range(5):
+                ref_step()
+            torch.cuda.synchronize(dev)
+            k = min(args.steps, 200)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(k):
+                ref_step()
+            b.record(stream)
+            torch.cuda.synchronize(dev)
+            rms = a.elapsed_time(b) / k
+            ref_gpu = {"kernel": "saga::adam_mixed, the reference's src/cuda/cuda_kernels.cu "
+                                 "compiled unmodified for sm_100a",
+                       "ms_per_step": rms, "value": n / (rms * 1e-3), "unit": "params/s",
+                       "hbm_gbs": 28 * n / (rms * 1e-3) / 1e9, "steps": k}
+            del rw, rg, rm, rv, rc_
 
     # ---- end to end through the C ABI: gradients start in pinned host memory,
     # every step copies them in, steps, waits, reads the flag sums back and
@@ -312,9 +368,9 @@ def main():
     clocks = sampler.stop() if sampler else None
 
     if world > 1:
-        t = torch.tensor([ms, e2e_s], dtype=torch.float64, device=dev)
+        t = torch.tensor([ms, e2e_s, nccl_ms or 0.0], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_s = float(t[0]), float(t[1])
+        ms, e2e_s, nccl_ms = float(t[0]), float(t[1]), float(t[2]) or None
 
     if rank == 0:
         per_step_ms = ms / args.steps
@@ -365,6 +421,14 @@ def main():
                 "frac": nv / NVLINK_MEASURED_GBS, "frac_of_900_nominal": nv / NVLINK_NOMINAL_GBS,
                 "bytes_per_direction_per_launch": nv_bytes,
             }
+            if nccl_ms:
+                line["nccl_sequence"] = {
+                    "what": "ncclReduceScatter + Adam kernel on the shard + ncclAllGather + "
+                            "3-word ncclAllReduce, the reference's call sequence, same buffers",
+                    "ms_per_step": nccl_ms, "speedup_of_fused_kernel": nccl_ms / per_step_ms}
+        if ref_gpu:
+            ref_gpu["speedup_of_fused_kernel"] = ref_gpu["ms_per_step"] / per_step_ms
+            line["ref_gpu"] = ref_gpu
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(n)
         print(json.dumps(line), flush=True)

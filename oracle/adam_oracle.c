@@ -470,6 +470,33 @@ orc_num_threads(void)
 #endif
 }
 
+/* Number of host threads the timed variants below use from now on. */
+void
+orc_set_num_threads(int n)
+{
+#ifdef _OPENMP
+    if(n > 0)
+        omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
+/* orc_reduce_half over all host threads: the gradient sum of a whole buffer
+ * (every shard) as the N-rank step needs it. */
+__attribute__((target("f16c"))) void
+orc_reduce_half_mt(int nranks, const uint16_t *const *g, size_t count,
+                   uint16_t *out)
+{
+#pragma omp parallel for schedule(static)
+    for(size_t i = 0; i < count; i++) {
+        float acc = _cvtsh_ss(g[0][i]);
+        for(int q = 1; q < nranks; q++)
+            acc += _cvtsh_ss(g[q][i]);
+        out[i] = nranks == 1 ? g[0][i] : _cvtss_sh(acc, _MM_FROUND_TO_NEAREST_INT);
+    }
+}
+
 /* Same arithmetic as orc_adam_mixed (model 1), elements split across all host
  * threads, half conversions through the CPU's F16C instructions as the
  * reference's host code does (src/fp16.h).  This is the CPU figure the

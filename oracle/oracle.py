@@ -56,6 +56,8 @@ def lib():
         L.orc_policy_reference.argtypes = [C.POINTER(C.c_float), _u32p]
         L.orc_policy_interval.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_int), _u32p, C.c_int]
         L.orc_num_threads.restype = C.c_int
+        L.orc_set_num_threads.argtypes = [C.c_int]
+        L.orc_reduce_half_mt.argtypes = [C.c_int, C.POINTER(C.c_void_p), C.c_size_t, _u16p]
         pp = C.POINTER(C.c_void_p)
         L.orc_step_multi.argtypes = [C.c_int, C.c_size_t, pp, pp, pp, pp, pp, C.c_size_t, pp, pp,
                                      pp, pp, C.c_int, C.c_float, C.c_float, C.c_float, _u32p,
@@ -132,6 +134,22 @@ def master_init(w_shard):
 
 def num_threads():
     return int(lib().orc_num_threads())
+
+
+def use_all_host_threads():
+    """Makes the timed variants use every core this process may run on (launchers
+    such as torchrun export OMP_NUM_THREADS=1)."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_num_threads(n)
+    return num_threads()
+
+
+def reduce_half_threads(grads, out):
+    """Rank-ordered fp32 sum of whole fp16 gradient buffers, all host threads."""
+    arr = (C.c_void_p * len(grads))(*[g.ctypes.data for g in grads])
+    lib().orc_reduce_half_mt(len(grads), arr, out.size, out)
+    return out
 
 
 class MultiRankState:

@@ -204,8 +204,12 @@ cudaError_t launch_staged(StepParams p, int num_sms, const LaunchTuning &t,
 //     2: 256 threads x 8 elements   3: 128 threads x 8 elements
 //     4: 256 threads x 4 elements   5: 512 threads x 4 elements
 //   variant 6: direct loads, two groups per thread per trip (one rank only)
-// Measured on a B200 at 25.6 M fp16 parameters, one rank: variant 4 with two
+// Measured on B200s at 25.6 M fp16 parameters.  One rank: variant 4 with two
 // CTAs per SM and four stages 114.9 us; best direct-load shape 119.4 us.
+// Several ranks over NVLink: every shape lands within a few percent of the
+// direct-load kernel (2 ranks 96.7 us, 4 ranks 136.8 us, 8 ranks 163.4 us; the
+// NCCL sequence of the reference takes 229.7 / 319.2 / 394.2 us), so the
+// simplest one, variant 1, is the default there.
 cudaError_t launch_step(const StepParams &p, int nranks, int num_sms,
                         const LaunchTuning &t, cudaStream_t st)
 {
@@ -234,7 +238,8 @@ cudaError_t launch_step(const StepParams &p, int nranks, int num_sms,
 #undef STAGED
     const size_t groups = std::max(p.h.ngroups, p.f.ngroups);
     const int unr = (nranks == 1 && variant == 6) ? 2 : 1;
-    const long def_ctas = 2;
+    // measured at 25.6 M parameters: 2 CTAs per SM up to four ranks, 3 beyond
+    const long def_ctas = nranks <= 4 ? 2 : 3;
     const long cps = ctas_per_sm > 0 ? ctas_per_sm : def_ctas;
     size_t want = (groups + (size_t)kThreads * unr - 1) / ((size_t)kThreads * unr);
     if(want == 0)
