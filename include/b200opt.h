@@ -197,6 +197,35 @@ B200OPT_API int b200opt_step_host(b200opt_t *h, const void *grads_half,
                       float scale, void *stream, uint32_t flags_out[3]);
 
 /*
+ * Loss scale resident on the device: removes the per-step host synchronise
+ * that CudaProgram::step needs to read the flags and update m_mp_scaling
+ * (src/cuda/cuda_program.cpp:293-302).  After b200opt_device_scale_enable the
+ * scale lives in this rank's control page; b200opt_step_device_scale takes
+ * 1/scale from there and the step kernel's last CTA applies the policy (same
+ * float-state, double-factor arithmetic) to it once the flag sums are known,
+ * so steps can be enqueued back to back without the host in the loop.  Every
+ * rank computes the same scale from the same sums.
+ *   b200opt_device_scale_ptr   device address of the live scale, for the
+ *                              kernels that multiply the loss gradient by it
+ *                              (src/cuda/cuda_dnn.cpp:1315,1428-1443 pass it
+ *                              by value today)
+ *   b200opt_device_scale_read  waits for `stream`; returns the current scale
+ *                              and the log of the last `log_capacity` steps,
+ *                              oldest first, four words per step:
+ *                              {range, inf, nan, bits of the scale after it}
+ * Not available in serial mode or on the NCCL path.
+ */
+B200OPT_API int b200opt_device_scale_enable(b200opt_t *h, float initial_scale,
+                                            int policy, int interval,
+                                            size_t log_capacity);
+B200OPT_API int b200opt_device_scale_ptr(b200opt_t *h, const float **scale_dev);
+B200OPT_API int b200opt_step_device_scale(b200opt_t *h, float lr,
+                                          float l2_lambda, void *stream);
+B200OPT_API int b200opt_device_scale_read(b200opt_t *h, void *stream,
+                                          float *scale, uint32_t *log_out,
+                                          size_t capacity, size_t *count);
+
+/*
  * Waits for `stream`, then returns the sums over ranks of {range, inf, nan}
  * raised by the last step and clears them: the values CudaProgram::step reads
  * from m_aux after its stream synchronise (src/cuda/cuda_program.cpp:293-306).

@@ -5,6 +5,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cstddef>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -67,6 +68,9 @@ struct b200opt {
     long nccl_crossover = 0;
     uint64_t launches = 0;
     NcclPath *nccl = nullptr;
+    bool device_scale = false;   // loss scale lives in the control page
+    uint32_t *scale_log = nullptr;
+    uint32_t scale_log_cap = 0;
     std::string err;
 };
 
@@ -434,6 +438,7 @@ int b200opt_destroy(b200opt_t *h)
     }
     cudaFree(h->arena);
     cudaFree(h->state);
+    cudaFree(h->scale_log);
     if(h->host)
         cudaFreeHost(h->host);
     delete h;
@@ -594,11 +599,14 @@ int b200opt_init_master(b200opt_t *h, void *stream)
     return B200OPT_OK;
 }
 
-int b200opt_step(b200opt_t *h, float lr, float l2_lambda, float scale,
-                 void *stream)
+static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
+                     bool device_scale, void *stream)
 {
     if(!h)
         return B200OPT_EINVAL;
+    if(device_scale && !h->device_scale)
+        return fail(h, B200OPT_ESTATE,
+                    "b200opt_device_scale_enable has not been called");
     if(h->failed)
         return fail(h, B200OPT_ESTATE,
                     "an earlier step timed out; the handle is unusable");
@@ -613,6 +621,9 @@ int b200opt_step(b200opt_t *h, float lr, float l2_lambda, float scale,
     memset(&p, 0, sizeof(p));
     b200opt_bias_corrections(iter, &p.b1t, &p.b2t);
     p.alpha = 1.0f / scale;
+    p.device_scale = device_scale ? 1 : 0;
+    p.scale_log = h->scale_log;
+    p.scale_log_cap = h->scale_log_cap;
     p.lr = lr;
     p.l2 = l2_lambda;
     p.rank = h->rank;
@@ -626,6 +637,9 @@ int b200opt_step(b200opt_t *h, float lr, float l2_lambda, float scale,
          (h->path == B200OPT_PATH_AUTO && h->nccl &&
           (long)h->n_half < h->nccl_crossover));
     if(use_nccl) {
+        if(device_scale)
+            return fail(h, B200OPT_EUNSUPPORTED,
+                        "the device-resident loss scale needs the peer-kernel path");
         if(!h->nccl)
             return fail(h, B200OPT_ESTATE,
                         "NCCL path selected but b200opt_nccl_init was not called");
@@ -673,6 +687,112 @@ int b200opt_step(b200opt_t *h, float lr, float l2_lambda, float scale,
     p.barrier = (h->nranks > 1 && !h->serial) ? 1 : 0;
     CK(h, launch_step(p, h->nranks, h->num_sms, tuning_of(h), st));
     h->launches++;
+    return B200OPT_OK;
+}
+
+int b200opt_step(b200opt_t *h, float lr, float l2_lambda, float scale,
+                 void *stream)
+{
+    return step_impl(h, lr, l2_lambda, scale, false, stream);
+}
+
+int b200opt_step_device_scale(b200opt_t *h, float lr, float l2_lambda,
+                              void *stream)
+{
+    return step_impl(h, lr, l2_lambda, 1.0f, true, stream);
+}
+
+int b200opt_device_scale_enable(b200opt_t *h, float initial_scale, int policy,
+                                int interval, size_t log_capacity)
+{
+    if(!h || !(initial_scale > 0) ||
+       (policy != B200OPT_POLICY_REFERENCE && policy != B200OPT_POLICY_INTERVAL) ||
+       (policy == B200OPT_POLICY_INTERVAL && interval < 1) ||
+       log_capacity > (1u << 24))
+        return B200OPT_EINVAL;
+    if(h->serial)
+        return fail(h, B200OPT_EUNSUPPORTED,
+                    "serial mode forms the flag sums on the host");
+    DeviceGuard guard(h->device);
+    CK(h, cudaDeviceSynchronize());
+    if(h->scale_log) {
+        cudaFree(h->scale_log);
+        h->scale_log = nullptr;
+        h->scale_log_cap = 0;
+    }
+    if(log_capacity) {
+        if(cudaMalloc(&h->scale_log, log_capacity * 16) != cudaSuccess)
+            return fail(h, B200OPT_ENOMEM, "cudaMalloc of the scale log");
+        CK(h, cudaMemset(h->scale_log, 0, log_capacity * 16));
+        h->scale_log_cap = (uint32_t)log_capacity;
+    }
+    Ctrl *ctrl = arena_ptr<Ctrl>(h->arena, 0);
+    struct {
+        float scale;
+        uint32_t policy;
+        int32_t clean;
+        int32_t interval;
+        uint32_t log_pos;
+    } init = {initial_scale, (uint32_t)policy, 0, interval, 0};
+    static_assert(offsetof(Ctrl, log_pos) - offsetof(Ctrl, scale) == 16,
+                  "device scale fields are contiguous");
+    CK(h, cudaMemcpy(&ctrl->scale, &init, sizeof(init), cudaMemcpyHostToDevice));
+    h->device_scale = true;
+    return B200OPT_OK;
+}
+
+int b200opt_device_scale_ptr(b200opt_t *h, const float **scale_dev)
+{
+    if(!h || !scale_dev)
+        return B200OPT_EINVAL;
+    if(!h->device_scale)
+        return fail(h, B200OPT_ESTATE,
+                    "b200opt_device_scale_enable has not been called");
+    *scale_dev = &arena_ptr<Ctrl>(h->arena, 0)->scale;
+    return B200OPT_OK;
+}
+
+int b200opt_device_scale_read(b200opt_t *h, void *stream, float *scale,
+                              uint32_t *log_out, size_t capacity, size_t *count)
+{
+    if(!h)
+        return B200OPT_EINVAL;
+    if(!h->device_scale)
+        return fail(h, B200OPT_ESTATE,
+                    "b200opt_device_scale_enable has not been called");
+    DeviceGuard guard(h->device);
+    CK(h, cudaStreamSynchronize((cudaStream_t)stream));
+    if(h->host->status) {
+        h->failed = true;
+        return fail(h, B200OPT_ETIMEOUT, "a step gave up waiting for a peer rank");
+    }
+    Ctrl *ctrl = arena_ptr<Ctrl>(h->arena, 0);
+    struct {
+        float scale;
+        uint32_t policy;
+        int32_t clean;
+        int32_t interval;
+        uint32_t log_pos;
+    } cur;
+    CK(h, cudaMemcpy(&cur, &ctrl->scale, sizeof(cur), cudaMemcpyDeviceToHost));
+    if(scale)
+        *scale = cur.scale;
+    // the ring holds the last scale_log_cap steps, oldest first
+    size_t have = std::min<size_t>(cur.log_pos, h->scale_log_cap);
+    if(count)
+        *count = have;
+    if(log_out && have) {
+        if(capacity < have)
+            return B200OPT_EINVAL;
+        const size_t cap = h->scale_log_cap;
+        const size_t first = (cur.log_pos - have) % cap;
+        const size_t run = std::min(have, cap - first);
+        CK(h, cudaMemcpy(log_out, h->scale_log + 4 * first, run * 16,
+                         cudaMemcpyDeviceToHost));
+        if(run < have)
+            CK(h, cudaMemcpy(log_out + 4 * run, h->scale_log, (have - run) * 16,
+                             cudaMemcpyDeviceToHost));
+    }
     return B200OPT_OK;
 }
 

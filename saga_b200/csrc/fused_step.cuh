@@ -53,7 +53,13 @@ struct alignas(128) Ctrl {
     uint32_t status;           // sticky B200OPT_E* (as positive number) or 0
     uint32_t pad0;
     uint32_t coll_flags[4];    // NCCL path: {range, inf, nan} to be all-reduced
-    uint32_t pad[24];
+    // device-resident loss scale (optional): updated by the last CTA of a step
+    float scale;               // current loss scale
+    uint32_t policy;           // B200OPT_POLICY_*
+    int32_t clean_steps;       // interval policy: clean steps since the last change
+    int32_t interval;          // interval policy: growth interval
+    uint32_t log_pos;          // steps logged so far
+    uint32_t pad[19];
 };
 
 // Written by the last CTA of a launch, read by the host after a stream sync.
@@ -96,7 +102,52 @@ struct StepParams {
     HostResult *host;       // pinned, may be null
     uint32_t *aux;          // kernel-seam mode: store 1 into aux[0..2], no ctrl
     uint32_t *flags_dev;    // NCCL path: this rank's {range, inf, nan} as 0/1
+    int device_scale;       // 1: 1/scale comes from ctrl[rank]->scale, and the last
+                            // CTA applies the loss-scale policy to it
+    uint32_t *scale_log;    // ring of {range, inf, nan, bits of the new scale} per step
+    uint32_t scale_log_cap; // entries in the ring (0: no log)
 };
+
+// 1/scale of this step: from the launch arguments, or from the scale that
+// lives in device memory (the reference divides in float,
+// src/cuda/cuda_optimizer.cpp:169 of the Saga tree).
+__device__ __forceinline__ float step_alpha(const StepParams &p)
+{
+    if(!p.device_scale)
+        return p.alpha;
+    const float s = *reinterpret_cast<const volatile float *>(&p.ctrl[p.rank]->scale);
+    return __fdiv_rn(1.0f, s);
+}
+
+// CudaProgram::step's policy (src/cuda/cuda_program.cpp:295-302 of the Saga
+// tree) evaluated on the device: float state, double factors.
+__device__ __forceinline__ void device_scale_update(const StepParams &p, Ctrl *my,
+                                                    const uint32_t (&sums)[3])
+{
+    float s = my->scale;
+    const bool overflow = sums[1] != 0 || sums[2] != 0;
+    if(my->policy == B200OPT_POLICY_INTERVAL) {
+        if(overflow) {
+            s = (float)((double)s * 0.5);
+            my->clean_steps = 0;
+        } else if(++my->clean_steps >= my->interval) {
+            s = (float)((double)s * 2.0);
+            my->clean_steps = 0;
+        }
+    } else {
+        const double factor = overflow ? 0.5 : (sums[0] > 1 ? 0.9 : 1.02);
+        s = (float)((double)s * factor);
+    }
+    my->scale = s;
+    if(p.scale_log_cap) {
+        uint32_t *e = p.scale_log + 4 * (size_t)(my->log_pos % p.scale_log_cap);
+        e[0] = sums[0];
+        e[1] = sums[1];
+        e[2] = sums[2];
+        e[3] = __float_as_uint(s);
+    }
+    my->log_pos++;
+}
 
 // ---------------------------------------------------------------- memory ops
 
@@ -224,7 +275,7 @@ __device__ __forceinline__ uint32_t float_to_half_bits(float f)
 // the owner's current fp16 weights of these elements (read only when an
 // element is skipped and must keep its weight).
 template <int VEC>
-__device__ __forceinline__ void half_update(const StepParams &p,
+__device__ __forceinline__ void half_update(const StepParams &p, float alpha,
                                             const uint32_t (&u)[VEC],
                                             float (&m)[VEC], float (&v)[VEC],
                                             float (&c)[VEC],
@@ -238,7 +289,7 @@ __device__ __forceinline__ void half_update(const StepParams &p,
     if(!any) {
 #pragma unroll
         for(int e = 0; e < VEC; e++) {
-            const float dw = __fmul_rn(half_bits_to_float(u[e]), p.alpha);
+            const float dw = __fmul_rn(half_bits_to_float(u[e]), alpha);
             adam_element<true>(dw, m[e], v[e], c[e], p.b1t, p.b2t, p.lr, p.l2);
             wbits[e] = float_to_half_bits(c[e]);
         }
@@ -249,7 +300,7 @@ __device__ __forceinline__ void half_update(const StepParams &p,
         if(classify_half(u[e], fl)) {
             wbits[e] = wold[e];  // skipped: m, v, master and weight stay
         } else {
-            const float dw = __fmul_rn(half_bits_to_float(u[e]), p.alpha);
+            const float dw = __fmul_rn(half_bits_to_float(u[e]), alpha);
             adam_element<true>(dw, m[e], v[e], c[e], p.b1t, p.b2t, p.lr, p.l2);
             wbits[e] = float_to_half_bits(c[e]);
         }
@@ -318,7 +369,8 @@ __device__ __forceinline__ void halves8(const uint4 &g, uint32_t (&u)[8])
 // Reduces, classifies and updates one 8-element group held in registers.
 // out[0..1] = m, out[2..3] = v, out[4..5] = master, out[6] = fp16 weights.
 template <int NR>
-__device__ __forceinline__ void half_compute(const StepParams &p, size_t idx0,
+__device__ __forceinline__ void half_compute(const StepParams &p, float alpha,
+                                             size_t idx0,
                                              const HalfLoads<NR> &L,
                                              uint32_t &fl, uint4 (&out)[7])
 {
@@ -349,7 +401,7 @@ __device__ __forceinline__ void half_compute(const StepParams &p, size_t idx0,
     unpack8(L.c0, L.c1, c);
 
     uint32_t wbits[8];
-    half_update<8>(p, u, m, v, c, wbits, p.h.W[p.rank] + idx0, fl);
+    half_update<8>(p, alpha, u, m, v, c, wbits, p.h.W[p.rank] + idx0, fl);
     pack8(m, out[0], out[1]);
     pack8(v, out[2], out[3]);
     pack8(c, out[4], out[5]);
@@ -359,12 +411,12 @@ __device__ __forceinline__ void half_compute(const StepParams &p, size_t idx0,
 
 template <int NR>
 __device__ __forceinline__ void half_compute_store(const StepParams &p,
-                                                   size_t idx0,
+                                                   float alpha, size_t idx0,
                                                    const HalfLoads<NR> &L,
                                                    uint32_t &fl)
 {
     uint4 out[7];
-    half_compute<NR>(p, idx0, L, fl, out);
+    half_compute<NR>(p, alpha, idx0, L, fl, out);
     const size_t li = idx0 - p.h.A;
     st_stream(p.h.m + li, out[0]);
     st_stream(p.h.m + li + 4, out[1]);
@@ -380,7 +432,8 @@ __device__ __forceinline__ void half_compute_store(const StepParams &p,
 // Element-wise path for the (at most two) groups that straddle a shard edge,
 // and for unaligned caller memory in kernel-seam mode.
 template <int NR>
-__device__ __noinline__ uint32_t half_scalar(const StepParams &p, size_t idx0)
+__device__ __noinline__ uint32_t half_scalar(const StepParams &p, float alpha,
+                                             size_t idx0)
 {
     uint32_t fl = 0;
     for(int e = 0; e < kVec; e++) {
@@ -399,7 +452,7 @@ __device__ __noinline__ uint32_t half_scalar(const StepParams &p, size_t idx0)
             continue;
         const size_t li = i - p.h.A;
         float m = p.h.m[li], v = p.h.v[li], c = p.h.c[li];
-        const float dw = __fmul_rn(half_bits_to_float(u), p.alpha);
+        const float dw = __fmul_rn(half_bits_to_float(u), alpha);
         adam_element<true>(dw, m, v, c, p.b1t, p.b2t, p.lr, p.l2);
         p.h.m[li] = m;
         p.h.v[li] = v;
@@ -656,6 +709,8 @@ __device__ __forceinline__ void step_finish(const StepParams &p, uint32_t fl,
         }
     }
     if(tid == 0) {
+        if(p.device_scale && !status)
+            device_scale_update(p, my, sums);
         if(p.flags_dev) {
             p.flags_dev[0] = sums[0];
             p.flags_dev[1] = sums[1];
@@ -686,6 +741,7 @@ __global__ void __launch_bounds__(kThreads, MINB)
     const int tid = threadIdx.x;
     uint32_t fl = 0;
     if(!step_begin<NR>(p)) {
+        const float alpha = step_alpha(p);
         const size_t stride = (size_t)gridDim.x * kThreads * UNR;
         const size_t ng = p.h.ngroups;
         const size_t lo = p.h.o, hi = p.h.o + p.h.s;
@@ -707,9 +763,9 @@ __global__ void __launch_bounds__(kThreads, MINB)
                 const size_t gid = base + (size_t)k * kThreads + tid;
                 const size_t idx0 = p.h.A + gid * kVec;
                 if(full[k])
-                    half_compute_store<NR>(p, idx0, L[k], fl);
+                    half_compute_store<NR>(p, alpha, idx0, L[k], fl);
                 else if(gid < ng)
-                    fl |= half_scalar<NR>(p, idx0);
+                    fl |= half_scalar<NR>(p, alpha, idx0);
             }
         }
         float_group_pass<NR>(p, fl);

@@ -167,7 +167,7 @@ __device__ __forceinline__ void sts_floats(unsigned char *base, int tid,
 
 // Updates, in place in one filled stage, the VEC elements this thread owns.
 template <int NR, int VEC, int TILE>
-__device__ __forceinline__ void staged_update(const StepParams &p,
+__device__ __forceinline__ void staged_update(const StepParams &p, float alpha,
                                               unsigned char *st, int tid,
                                               size_t gidx, uint32_t &fl)
 {
@@ -199,7 +199,7 @@ __device__ __forceinline__ void staged_update(const StepParams &p,
     lds_floats<VEC>(st + kOffV, tid, v);
     lds_floats<VEC>(st + kOffC, tid, c);
     uint32_t wbits[VEC];
-    half_update<VEC>(p, u, m, v, c, wbits, p.h.W[p.rank] + gidx, fl);
+    half_update<VEC>(p, alpha, u, m, v, c, wbits, p.h.W[p.rank] + gidx, fl);
     sts_floats<VEC>(st + kOffM, tid, m);
     sts_floats<VEC>(st + kOffV, tid, v);
     sts_floats<VEC>(st + kOffC, tid, c);
@@ -235,6 +235,7 @@ __global__ void __launch_bounds__(THREADS)
 
     uint32_t fl = 0;
     if(!step_begin<NR>(p)) {
+        const float alpha = step_alpha(p);
         // full 8-element groups of the shard: [F0, F1); the (at most two)
         // ragged groups at the shard's ends go through the element-wise path
         const size_t lo = p.h.o, hi = p.h.o + p.h.s;
@@ -299,8 +300,8 @@ __global__ void __launch_bounds__(THREADS)
             const uint32_t te = tile_elems(k);
             const size_t e0 = tile_start(k);
             if((uint32_t)tid * VEC < te) {
-                staged_update<NR, VEC, TILE>(p, st, tid, e0 + (size_t)tid * VEC,
-                                             fl);
+                staged_update<NR, VEC, TILE>(p, alpha, st, tid,
+                                             e0 + (size_t)tid * VEC, fl);
                 fence_proxy_async_smem();
             }
             __syncthreads();
@@ -346,12 +347,12 @@ __global__ void __launch_bounds__(THREADS)
             const size_t ng = p.h.ngroups;
             for(size_t gid = (size_t)blockIdx.x * THREADS + tid; gid < ng;
                 gid += (size_t)gridDim.x * THREADS)
-                fl |= half_scalar<NR>(p, p.h.A + gid * kVec);
+                fl |= half_scalar<NR>(p, alpha, p.h.A + gid * kVec);
         } else if(blockIdx.x == 0 && p.h.s) {
             if(tid == 0 && lo != F0)
-                fl |= half_scalar<NR>(p, lo & ~(size_t)(kVec - 1));
+                fl |= half_scalar<NR>(p, alpha, lo & ~(size_t)(kVec - 1));
             if(tid == 1 && F1 < hi && F1 >= F0)
-                fl |= half_scalar<NR>(p, F1);
+                fl |= half_scalar<NR>(p, alpha, F1);
         }
         float_group_pass<NR>(p, fl);
     }

@@ -184,6 +184,33 @@ class AdamGroup:
         check(lib().b200opt_flags(self._h, C.c_void_p(stream), out), self._h)
         return (out[0], out[1], out[2])
 
+    # ------------------------------------------- loss scale kept on the device
+    def device_scale_enable(self, initial_scale, policy=capi.POLICY_REFERENCE, interval=2000,
+                            log_capacity=4096):
+        check(lib().b200opt_device_scale_enable(self._h, float(initial_scale), policy, interval,
+                                                log_capacity), self._h)
+
+    def device_scale_ptr(self):
+        p = C.c_void_p()
+        check(lib().b200opt_device_scale_ptr(self._h, C.byref(p)), self._h)
+        return p.value
+
+    def exec_device_scale(self, lr, l2_lambda, stream=0):
+        """Like exec, with 1/scale read from and the policy applied on the device."""
+        check(lib().b200opt_step_device_scale(self._h, lr, l2_lambda, C.c_void_p(stream)), self._h)
+
+    def device_scale_read(self, stream=0, capacity=4096):
+        """(scale, log) after waiting for the stream; log rows = (range, inf, nan, scale)."""
+        scale, cnt = C.c_float(), C.c_size_t()
+        buf = np.zeros((capacity, 4), dtype=np.uint32)
+        check(lib().b200opt_device_scale_read(self._h, C.c_void_p(stream), C.byref(scale),
+                                              buf.ctypes.data_as(C.c_void_p), capacity,
+                                              C.byref(cnt)), self._h)
+        rows = buf[:cnt.value]
+        log = [(int(r[0]), int(r[1]), int(r[2]), np.float32(r[3:4].view(np.float32)[0]))
+               for r in rows]
+        return np.float32(scale.value), log
+
     def step_host(self, grads_half_ptr, grads_float_ptr, lr, l2_lambda, scale, stream=0):
         out = (C.c_uint32 * 3)()
         check(lib().b200opt_step_host(self._h, C.c_void_p(grads_half_ptr),
