@@ -1,0 +1,136 @@
+"""Builds the two end-to-end training binaries (needs the Saga checkout):
+
+  oracle/_ref/saga_e2e_ref    the reference library, unmodified (NCCL build),
+                              + its own test/test_classifier.cpp + e2e_main.cpp
+  oracle/_ref/saga_e2e_b200   the same with the optimizer ops replaced by the
+                              b200opt op: the library sources are copied to a
+                              scratch directory outside this repository and
+                              edited there by the small anchored rewrites below
+
+    python saga_b200/host/e2e/build_saga_e2e.py [/path/to/saga]
+
+Nothing of the reference's source is stored in this repository; the rewrites
+name only the identifiers they hang on.
+"""
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.abspath(os.path.join(HERE, "..", "..", ".."))
+OUT = os.path.join(ROOT, "oracle", "_ref")
+
+LIB_SRCS = ["src/util.cpp", "src/tensor.cpp", "src/graph.cpp", "src/node.cpp", "src/engine.cpp",
+            "src/ui/tui.cpp", "src/ui/nui.cpp", "src/pub.cpp",
+            "src/cuda/cuda_common.cpp", "src/cuda/cuda_program.cpp", "src/cuda/cuda_analysis.cpp",
+            "src/cuda/cuda_dnn.cpp", "src/cuda/cuda_optimizer.cpp", "src/cuda/cuda_tensor.cpp"]
+KERNELS = "src/cuda/cuda_kernels.cu"
+HARNESS = "test/test_classifier.cpp"
+
+CXX = ["g++", "--std=c++17", "-O2", "-fPIC", "-mf16c", "-Wno-deprecated-declarations",
+       "-Wno-terminate", "-I/usr/local/cuda/include"]
+NVCC = ["/usr/local/cuda/bin/nvcc", "--std=c++17", "-O2", "-gencode",
+        "arch=compute_100a,code=sm_100a", "-Xcompiler", "-fPIC"]
+LIBS = ["-L/usr/local/cuda/lib64", "-lcudart", "-lcudnn", "-lcublas", "-lpthread"]
+
+
+def run(cmd):
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(" ".join(cmd) + "\n" + res.stdout[-3000:] + res.stderr[-6000:])
+        raise SystemExit(1)
+
+
+def rewrite(path, edits):
+    text = open(path).read()
+    for fn in edits:
+        text = fn(text)
+    open(path, "w").write(text)
+
+
+def patch_tree(tree):
+    """The b200opt integration, as edits anchored on identifiers of the Saga tree."""
+    def storage_hpp(t):
+        a = "CudaTensorStorageMemory(size_t size);"
+        assert a in t
+        return t.replace(a, a + "\n    CudaTensorStorageMemory(void *external, int)"
+                                " : m_mem(external), m_external(true) {}\n"
+                                "    bool m_external{false};", 1)
+
+    def storage_cpp(t):
+        a = "chkCuda(cudaFree(m_mem));"
+        assert a in t
+        return t.replace(a, "if(!m_external)\n        " + a, 1)
+
+    def optimizer_cpp(t):
+        start = t.index("CudaOps\nCudaProgram::create_optimizers()")
+        end = t.rindex("}  // namespace saga")
+        head = t[:start].replace('#include "cuda_kernels.hpp"',
+                                 '#include "cuda_kernels.hpp"\n#include <mutex>\n#include <map>\n'
+                                 '#include "cuda_aux.hpp"\n#include "b200_adam_op.hpp"', 1)
+        return head + '#include "b200_create_optimizers.inc"\n\n' + t[end:]
+
+    def program_cpp(t):
+        pos = t.index("m_mp_scaling *= 0.5")
+        start = t.rindex("if(m_mp_enabled)", 0, pos)
+        t = t[:start] + "b200_fill_aux(*this);\n\n    " + t[start:]
+        a = "namespace saga {"
+        i = t.index(a)
+        return t[:i] + a + "\nclass CudaProgram;\nvoid b200_fill_aux(CudaProgram &p);\n" + t[i + len(a):]
+
+    rewrite(os.path.join(tree, "src/cuda/cuda_tensor.hpp"), [storage_hpp])
+    rewrite(os.path.join(tree, "src/cuda/cuda_tensor.cpp"), [storage_cpp])
+    rewrite(os.path.join(tree, "src/cuda/cuda_optimizer.cpp"), [optimizer_cpp])
+    rewrite(os.path.join(tree, "src/cuda/cuda_program.cpp"), [program_cpp])
+
+
+def build_variant(ref, work, name, defines, extra_inc, extra_libs):
+    objs = []
+    inc = ["-I" + ref, "-I" + os.path.join(ref, "src")] + extra_inc
+    procs = []
+    for src in LIB_SRCS + [HARNESS]:
+        obj = os.path.join(work, name + "_" + src.replace("/", "_") + ".o")
+        objs.append(obj)
+        procs.append(subprocess.Popen(CXX + defines + inc + ["-c", os.path.join(ref, src), "-o", obj],
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    kobj = os.path.join(work, name + "_kernels.o")
+    run(NVCC + ["-I" + os.path.join(ref, "src", "cuda"), "-c", os.path.join(ref, KERNELS), "-o", kobj])
+    mobj = os.path.join(work, name + "_main.o")
+    run(CXX + defines + inc + ["-c", os.path.join(HERE, "e2e_main.cpp"), "-o", mobj])
+    for p in procs:
+        out, _ = p.communicate()
+        if p.returncode != 0:
+            sys.stderr.write(out[-8000:])
+            raise SystemExit(1)
+    # link order follows the reference's Makefile: library objects, kernels, programs
+    lib_objs, harness_obj = objs[:-1], objs[-1]
+    exe = os.path.join(OUT, name)
+    run(["g++", "-o", exe] + lib_objs + [kobj, mobj, harness_obj] + LIBS + extra_libs)
+    return exe
+
+
+def main():
+    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if not os.path.exists(os.path.join(ref, "saga.hpp")):
+        print(f"Saga checkout not found at {ref}: keeping any prebuilt binaries")
+        return
+    os.makedirs(OUT, exist_ok=True)
+    work = tempfile.mkdtemp(prefix="saga_e2e_")
+    try:
+        print(build_variant(ref, work, "saga_e2e_ref", ["-DHAVE_NCCL"], [], ["-lnccl"]))
+        tree = os.path.join(work, "tree")
+        shutil.copytree(ref, tree, ignore=shutil.ignore_patterns(".git", "build"))
+        patch_tree(tree)
+        libdir = os.path.join(ROOT, "saga_b200")
+        print(build_variant(tree, work, "saga_e2e_b200", ["-DHAVE_B200OPT"],
+                            ["-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(ROOT, "saga_b200", "host"),
+                             "-I" + HERE],
+                            ["-L" + libdir, "-lb200opt", "-Wl,-rpath,$ORIGIN/../../saga_b200"]))
+    finally:
+        shutil.rmtree(work, ignore_errors=True)
+
+
+if __name__ == "__main__":
+    main()
