@@ -62,7 +62,7 @@ extern "C" {
 #define B200OPT_OPT_TIMEOUT_MS 1    /* limit of every cross-GPU wait (default 10000) */
 #define B200OPT_OPT_PATH 2          /* B200OPT_PATH_* */
 #define B200OPT_OPT_CTAS_PER_SM 3   /* launch shape of the fused kernel (tuning) */
-#define B200OPT_OPT_KERNEL_VARIANT 4 /* 0 = default; 1,6 = direct 16-byte loads; 2..5 = bulk-copy staging through shared memory */
+#define B200OPT_OPT_KERNEL_VARIANT 4 /* 0 = default; 1,6 = direct 16-byte loads; 2..5 = bulk-copy staging through shared memory; 7..10 = the same with one ring per warp */
 #define B200OPT_OPT_NCCL_CROSSOVER 5 /* AUTO uses NCCL when n_half is below this many elements */
 #define B200OPT_OPT_STAGES 6        /* depth of the shared-memory ring of the staged kernel (tuning) */
 #define B200OPT_OPT_GRID 7          /* number of CTAs of the step kernel, overrides CTAS_PER_SM (tuning) */

@@ -15,6 +15,7 @@
 
 #include "fused_step.cuh"
 #include "staged_step.cuh"
+#include "warp_ring_step.cuh"
 #include "nccl_path.h"
 
 using namespace b200;
@@ -200,6 +201,47 @@ cudaError_t launch_staged(StepParams p, int num_sms, const LaunchTuning &t,
     return cudaGetLastError();
 }
 
+template <int NR, int VEC, int WARPS>
+cudaError_t launch_warp_ring(StepParams p, int num_sms, const LaunchTuning &t,
+                             int def_stages, int def_ctas, cudaStream_t st)
+{
+    constexpr int TILE = 32 * VEC;
+    constexpr size_t per_stage = stage_bytes(NR, TILE) * WARPS;  // per CTA
+    const size_t budget = 227 * 1024 - 4096;
+    const long cps = t.ctas_per_sm > 0 ? t.ctas_per_sm : def_ctas;
+    int stages = (int)(t.stages > 0 ? t.stages : def_stages);
+    while(stages > 1 && (size_t)stages * per_stage * (size_t)cps > budget)
+        stages--;
+    if(stages > kMaxWarpStages)
+        stages = kMaxWarpStages;
+    const size_t smem = (size_t)stages * per_stage;
+    if(smem > budget)
+        return cudaErrorInvalidValue;
+    auto kern = warp_ring_step_kernel<NR, VEC, WARPS>;
+    static std::atomic<uint64_t> opted{0};
+    int dev = 0;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if(ce != cudaSuccess)
+        return ce;
+    if(dev >= 64 || !(opted.load() & (1ull << dev))) {
+        ce = cudaFuncSetAttribute(
+            kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+        if(ce != cudaSuccess)
+            return ce;
+        if(dev < 64)
+            opted.fetch_or(1ull << dev);
+    }
+    const size_t cta_elems = (size_t)TILE * WARPS;
+    const size_t tiles_h = (p.h.ngroups * kVec + cta_elems - 1) / cta_elems;
+    const size_t tiles_f = (p.f.ngroups + WARPS * 32 - 1) / (WARPS * 32);
+    size_t want = std::max<size_t>(std::max(tiles_h, tiles_f), 1);
+    const size_t cap = t.grid > 0 ? (size_t)t.grid : (size_t)num_sms * cps;
+    const int grid = (int)std::min<size_t>(want, cap);
+    p.stages = stages;
+    kern<<<grid, WARPS * 32, smem, st>>>(p);
+    return cudaGetLastError();
+}
+
 // Launch shape: a persistent grid of ctas_per_sm CTAs on every SM, shrunk for
 // small inputs so that no CTA starts without work.
 //   variant 0: the default of the rank count (4 for one rank)
@@ -208,6 +250,9 @@ cudaError_t launch_staged(StepParams p, int num_sms, const LaunchTuning &t,
 //     2: 256 threads x 8 elements   3: 128 threads x 8 elements
 //     4: 256 threads x 4 elements   5: 512 threads x 4 elements
 //   variant 6: direct loads, two groups per thread per trip (one rank only)
+//   variants 7..10: bulk-copy staging with one ring per warp (1, 2, 4, 8 ranks)
+//     7: 8 warps x 8 elements/lane    8: 16 warps x 8
+//     9: 16 warps x 4                10: 32 warps x 4
 // Measured on B200s at 25.6 M fp16 parameters.  One rank: variant 4 with two
 // CTAs per SM and four stages 114.9 us; best direct-load shape 119.4 us.
 // Several ranks over NVLink: every shape lands within a few percent of the
@@ -226,6 +271,23 @@ cudaError_t launch_step(const StepParams &p, int nranks, int num_sms,
     case 4: return launch_staged<NR, 4, 256>(p, num_sms, t, 4, 2, st);     \
     default: return launch_staged<NR, 4, 512>(p, num_sms, t, 4, 1, st);    \
     }
+#define WARP_RING(NR)                                                        \
+    switch(variant) {                                                        \
+    case 7: return launch_warp_ring<NR, 8, 8>(p, num_sms, t, 4, 2, st);      \
+    case 8: return launch_warp_ring<NR, 8, 16>(p, num_sms, t, 4, 1, st);     \
+    case 9: return launch_warp_ring<NR, 4, 16>(p, num_sms, t, 4, 2, st);     \
+    default: return launch_warp_ring<NR, 4, 32>(p, num_sms, t, 4, 1, st);    \
+    }
+    if(variant >= 7 && variant <= 10) {
+        switch(nranks) {
+        case 1: WARP_RING(1)
+        case 2: WARP_RING(2)
+        case 4: WARP_RING(4)
+        case 8: WARP_RING(8)
+        }
+        return cudaErrorInvalidValue;
+    }
+#undef WARP_RING
     if(variant >= 2 && variant <= 5) {
         switch(nranks) {
         case 1: STAGED(1)
@@ -1114,7 +1176,7 @@ int b200opt_set_option(b200opt_t *h, int option, long value)
         h->ctas_per_sm = value;
         return B200OPT_OK;
     case B200OPT_OPT_KERNEL_VARIANT:
-        if(value < 0 || value > 6)
+        if(value < 0 || value > 10)
             return B200OPT_EINVAL;
         h->variant = value;
         return B200OPT_OK;

@@ -4,8 +4,8 @@
 // interface.  It is meant to be compiled INSIDE the Saga tree, included from
 // src/cuda/cuda_optimizer.cpp after that file's own includes ("saga.hpp",
 // "cuda_common.hpp", "cuda_tensor.hpp"), with -DHAVE_B200OPT and this
-// repository's include/ directory on the include path; see INTEGRATION.md for
-// the patch that uses it.
+// repository's include/ directory on the include path;
+// saga_b200/host/e2e/build_saga_e2e.py applies the edits that use it.
 //
 // What it mirrors (paths relative to the Saga project root):
 //   struct Optimizer / AdamF32 / AdamMixed   src/cuda/cuda_optimizer.cpp:37-194
@@ -81,7 +81,8 @@ private:
 // Non-owning view of library memory, so that tensor storages can alias it the
 // way they alias the reference's flat allocation
 // (src/cuda/cuda_optimizer.cpp:245-249).  Needs the one-line constructor
-// `CudaTensorStorageMemory(void *external)` that INTEGRATION.md adds.
+// `CudaTensorStorageMemory(void *external, int)` that the integration adds to
+// src/cuda/cuda_tensor.hpp.
 
 struct B200Adam : public CudaOperation {
     B200Adam(CudaProgram &p, b200opt_t *handle, const CudaOpArgs &inputs,

@@ -120,7 +120,7 @@ def compare_with_oracle(out, model):
 
 
 def main():
-    outdir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "gpurun_out", "golden")
+    outdir = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "golden_out")
     os.makedirs(outdir, exist_ok=True)
     report = {"gpu": torch.cuda.get_device_name(0)}
     for name, out in (
