@@ -483,3 +483,131 @@ def test_linearity_in_the_loss_scale(oracle):
         g.destroy()
     for a, b in zip(outs[0], outs[1]):
         assert np.array_equal(a, b)
+
+
+# --------------------------------------------------- long trajectories, big buffers
+
+@pytest.mark.parametrize("policy", ["reference", "interval"])
+def test_2100_steps_flags_and_scale_bit_exact(oracle, policy):
+    """2100 steps with an inf injected every 50th step.  Under the reference policy the
+    scale climbs x1.02 per clean step until gradients overflow on their own, then
+    saw-tooths; under the interval policy it halves on overflow and doubles after
+    2000 clean steps.  Every step's flag tuple and scale must equal the oracle's."""
+    n, steps = 1 << 14, 2100
+    W0 = synth.weights_half(n, seed=71)
+    prog = Program(1, n)
+    try:
+        prog.set_weights([W0])
+        ost = oracle.MultiRankState(1, [W0])
+        pol = capi.POLICY_REFERENCE if policy == "reference" else capi.POLICY_INTERVAL
+        gs = LossScaler(1024.0, policy=pol, interval=2000)
+        oscale, oclean = np.float32(1024.0), 0
+        seen = set()
+        halvings = doublings = 0
+        for step in range(1, steps + 1):
+            G = synth.grads_half(n, gs.scale, step, seed=71, inject_inf_every=50)
+            if policy == "interval" and step > 60:
+                G = synth.grads_half(n, gs.scale, step, seed=71)  # 2000 clean steps in a row
+            prog.set_grads([G])
+            flags = prog.step(1e-3, 0.0, gs.scale)
+            oflags = ost.step([G.copy()], None, oscale, 1e-3, 0.0)
+            assert flags == oflags, (step, flags, oflags)
+            seen.add(flags)
+            prev = gs.scale
+            gs.update(flags)
+            if policy == "reference":
+                oscale = oracle.policy_reference(oscale, oflags)
+            else:
+                oscale, oclean = oracle.policy_interval(oscale, oclean, oflags, 2000)
+            assert gs.scale.tobytes() == oscale.tobytes(), step
+            halvings += gs.scale < prev
+            doublings += gs.scale == np.float32(2) * prev
+        if policy == "reference":
+            # injected infs, natural overflows near the top of the saw-tooth, range-only steps
+            assert (1, 1, 0) in seen and (0, 0, 0) in seen and (1, 0, 0) in seen
+            assert halvings > 42      # more than the 42 injected ones: natural overflows too
+        else:
+            assert halvings == 1 and doublings == 1
+        assert synth.rel_err(prog.state(0, capi.HALF, 2), ost.c[0]) <= 1e-5
+    finally:
+        prog.close()
+
+
+def test_padding_stays_zero_across_eight_ranks(oracle):
+    """160 tensors padded to 16 elements, eight ranks: padding is zero in the weights of
+    every rank and in every rank's m, v and master after several steps."""
+    from saga_b200 import FlatLayout
+    nranks = 8
+    sizes = synth.tensor_sizes(1_000_000, 160, lo=8, hi=60000, seed=3)
+    lay = FlatLayout(sizes)
+    n = lay.total
+    real = np.zeros(n, dtype=bool)
+    for sl in lay.slices():
+        real[sl] = True
+    assert (~real).sum() > 500
+    W0 = synth.weights_half(n, seed=72)
+    W0[~real] = 0
+    prog = Program(nranks, n)
+    try:
+        prog.set_weights([W0] * nranks)
+        for step in range(1, 4):
+            G = []
+            for r in range(nranks):
+                g = synth.grads_half(n, 64.0, step, rank=r, seed=72)
+                g[~real] = 0
+                G.append(g)
+            prog.set_grads(G)
+            prog.step(1e-2, 0.01, 64.0)
+        s = n // nranks
+        for r in range(nranks):
+            assert not prog.weights_half(r)[~real].any()
+            pad = ~real[r * s:(r + 1) * s]
+            for which in range(3):
+                assert not prog.state(r, capi.HALF, which)[pad].any()
+        assert prog.weights_half(0)[real].any()
+    finally:
+        prog.close()
+
+
+def test_flat_buffer_of_2_30_elements(oracle):
+    """The largest size of the bandwidth sweep: 2^30 fp16 elements on one GPU (the
+    reference indexes with int; this path with size_t).  Checked through properties:
+    slices at the start, middle and end against the oracle, fp16 weights equal to the
+    rounded master everywhere, flags from an inf planted in the last element."""
+    n = 1 << 30
+    free, _ = torch.cuda.mem_get_info(0)
+    if free < 40 * (1 << 30):
+        pytest.skip("needs 40 GB of free device memory")
+    dev = torch.device("cuda", 0)
+    g = AdamGroup.create(0, 1, 0, n, 0)
+    try:
+        w, gr = g.buffers(capi.HALF)
+        chunk = 1 << 27
+        gen = torch.Generator(device=dev).manual_seed(5)
+        for c0 in range(0, n, chunk):
+            w[c0:c0 + chunk] = (torch.randn(chunk, device=dev, generator=gen) * 0.02).half()
+            gr[c0:c0 + chunk] = (torch.randn(chunk, device=dev, generator=gen) * 0.5).half()
+        gr[n - 1] = float("inf")
+        g.init_master(stream_ptr())
+        torch.cuda.synchronize()
+        slices = [(0, 1 << 16), (n // 2 - 12345, 1 << 16), (n - (1 << 16), 1 << 16)]
+        before = [(host_u16(w[a:a + k]), host_u16(gr[a:a + k])) for a, k in slices]
+        g.exec(1e-3, 0.01, 512.0, stream_ptr())
+        assert g.flags(stream_ptr()) == (1, 1, 0)
+        b1t, b2t = oracle.bias_corrections(1)
+        for (a, k), (w0, g0) in zip(slices, before):
+            ow, om, ov = w0.copy(), np.zeros(k, np.float32), np.zeros(k, np.float32)
+            oc = oracle.master_init(w0)
+            oracle.adam_mixed(ow, g0, om, ov, oc, oracle.alpha(512.0), b1t, b2t, 1e-3, 0.01)
+            assert np.array_equal(host_u16(w[a:a + k]), ow), a
+        # the planted inf: last element untouched
+        assert host_u16(w[n - 1:])[0] == before[2][0][-1]
+        # weights == half(master) over the whole buffer, chunk by chunk through the state export
+        c = g.export_state(capi.HALF, 2)
+        assert c.size == n
+        for c0 in range(0, n, chunk):
+            cc = torch.from_numpy(c[c0:c0 + chunk]).to(dev)
+            assert torch.equal(w[c0:c0 + chunk], cc.half())
+    finally:
+        w = gr = None
+        g.destroy()
