@@ -187,6 +187,33 @@ B200OPT_API int b200opt_step(b200opt_t *h, float lr, float l2_lambda, float scal
                  void *stream);
 
 /*
+ * One step issued as several buckets, so that the reduction and update of the
+ * gradients that backward has already finished can run (on a stream of the
+ * caller's choosing) while backward is still producing the others.  The
+ * reference can only start after ALL backward ops: its optimizer ops are
+ * appended behind them (src/cuda/cuda_program.cpp:455).
+ *   b200opt_step_begin   opens the step: advances the iteration counter once
+ *   b200opt_step_bucket  the fused reduce + update + gather for elements
+ *                        [first, first+count) of each dtype group's flat buffer
+ *                        (each rank does the part that lies in its shard).
+ *                        Every element must be covered by exactly one bucket
+ *                        of the step; every rank issues the same buckets in the
+ *                        same order; `last` != 0 marks the final bucket, whose
+ *                        kernel also completes the step across ranks (flag
+ *                        sums, all weights landed).  b200opt_flags after it.
+ * Buckets of one step give bit for bit the result of one b200opt_step.  With
+ * several ranks each bucket's kernel waits (bounded) until every rank has
+ * issued the same bucket, i.e. until that bucket's gradients are final
+ * everywhere.  Not available on the NCCL path.
+ */
+B200OPT_API int b200opt_step_begin(b200opt_t *h);
+B200OPT_API int b200opt_step_bucket(b200opt_t *h, size_t half_first,
+                                    size_t half_count, size_t float_first,
+                                    size_t float_count, float lr,
+                                    float l2_lambda, float scale, void *stream,
+                                    int last);
+
+/*
  * Same step, gradients taken from HOST memory: copies grads_half (n_half fp16)
  * and grads_float (n_float fp32) into the gradient buffers on `stream`, steps,
  * waits for the stream and returns the flag sums.  Either pointer may be NULL

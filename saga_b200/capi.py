@@ -41,6 +41,8 @@ SIGNATURES = {
     "b200opt_layout": (_i, [C.POINTER(_sz), _sz, C.POINTER(_sz), C.POINTER(_sz)]),
     "b200opt_init_master": (_i, [_vp, _vp]),
     "b200opt_step": (_i, [_vp, _f, _f, _f, _vp]),
+    "b200opt_step_begin": (_i, [_vp]),
+    "b200opt_step_bucket": (_i, [_vp, _sz, _sz, _sz, _sz, _f, _f, _f, _vp, _i]),
     "b200opt_step_host": (_i, [_vp, _vp, _vp, _f, _f, _f, _vp, _u32p]),
     "b200opt_flags": (_i, [_vp, _vp, _u32p]),
     "b200opt_device_scale_enable": (_i, [_vp, _f, _i, _i, _sz]),

@@ -70,6 +70,7 @@ struct b200opt {
     uint64_t launches = 0;
     NcclPath *nccl = nullptr;
     bool device_scale = false;   // loss scale lives in the control page
+    bool step_open = false;      // between b200opt_step_begin and the last bucket
     uint32_t *scale_log = nullptr;
     uint32_t scale_log_cap = 0;
     std::string err;
@@ -119,7 +120,26 @@ T *arena_ptr(char *base, size_t off)
     return base ? reinterpret_cast<T *>(base + off) : nullptr;
 }
 
-void fill_groups(const b200opt *h, StepParams &p)
+// Part of the flat buffers one launch works on: the whole shard, or the shard
+// clipped to [first, first + count) of each dtype group (a bucket of a step).
+struct StepRange {
+    bool whole = true;
+    size_t h_first = 0, h_count = 0, f_first = 0, f_count = 0;
+};
+
+void clip(size_t o, size_t s, bool whole, size_t first, size_t count, size_t *lo,
+          size_t *len)
+{
+    size_t a = o, b = o + s;
+    if(!whole) {
+        a = std::max(a, first);
+        b = std::min(b, first + count);
+    }
+    *lo = a;
+    *len = b > a ? b - a : 0;
+}
+
+void fill_groups(const b200opt *h, StepParams &p, const StepRange &r = StepRange())
 {
     for(int q = 0; q < h->nranks; q++) {
         char *base = h->peer_arena[q];
@@ -132,16 +152,16 @@ void fill_groups(const b200opt *h, StepParams &p)
     p.h.m = h->mh;
     p.h.v = h->vh;
     p.h.c = h->ch;
-    p.h.o = h->oh;
-    p.h.s = h->sh;
+    clip(h->oh, h->sh, r.whole, r.h_first, r.h_count, &p.h.o, &p.h.s);
     p.h.A = h->Ah;
-    p.h.ngroups = h->sh ? (h->oh + h->sh - h->Ah + kVec - 1) / kVec : 0;
+    p.h.B = p.h.o & ~(size_t)(kVec - 1);
+    p.h.ngroups = p.h.s ? (p.h.o + p.h.s - p.h.B + kVec - 1) / kVec : 0;
     p.f.m = h->mf;
     p.f.v = h->vf;
-    p.f.o = h->of;
-    p.f.s = h->sf;
+    clip(h->of, h->sf, r.whole, r.f_first, r.f_count, &p.f.o, &p.f.s);
     p.f.A = h->Af;
-    p.f.ngroups = h->sf ? (h->of + h->sf - h->Af + kVec - 1) / kVec : 0;
+    p.f.B = p.f.o & ~(size_t)(kVec - 1);
+    p.f.ngroups = p.f.s ? (p.f.o + p.f.s - p.f.B + kVec - 1) / kVec : 0;
 }
 
 template <int NR, int UNR, int MINB>
@@ -662,7 +682,9 @@ int b200opt_init_master(b200opt_t *h, void *stream)
 }
 
 static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
-                     bool device_scale, void *stream)
+                     bool device_scale, void *stream,
+                     const StepRange &range = StepRange(), bool begins = true,
+                     bool last = true)
 {
     if(!h)
         return B200OPT_EINVAL;
@@ -678,7 +700,9 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
     cudaStream_t st = (cudaStream_t)stream;
 
     // src/cuda/cuda_optimizer.cpp:150-152,169 of the Saga tree
-    const int iter = ++h->iter;
+    if(begins)
+        ++h->iter;
+    const int iter = h->iter;
     StepParams p;
     memset(&p, 0, sizeof(p));
     b200opt_bias_corrections(iter, &p.b1t, &p.b2t);
@@ -699,6 +723,9 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
          (h->path == B200OPT_PATH_AUTO && h->nccl &&
           (long)h->n_half < h->nccl_crossover));
     if(use_nccl) {
+        if(!range.whole)
+            return fail(h, B200OPT_EUNSUPPORTED,
+                        "bucketed steps need the peer-kernel path");
         if(device_scale)
             return fail(h, B200OPT_EUNSUPPORTED,
                         "the device-resident loss scale needs the peer-kernel path");
@@ -745,7 +772,8 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
         return B200OPT_OK;
     }
 
-    fill_groups(h, p);
+    fill_groups(h, p, range);
+    p.partial = last ? 0 : 1;
     p.barrier = (h->nranks > 1 && !h->serial) ? 1 : 0;
     CK(h, launch_step(p, h->nranks, h->num_sms, tuning_of(h), st));
     h->launches++;
@@ -755,7 +783,42 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
 int b200opt_step(b200opt_t *h, float lr, float l2_lambda, float scale,
                  void *stream)
 {
+    if(h && h->step_open)
+        return fail(h, B200OPT_ESTATE, "a bucketed step is open");
     return step_impl(h, lr, l2_lambda, scale, false, stream);
+}
+
+int b200opt_step_begin(b200opt_t *h)
+{
+    if(!h)
+        return B200OPT_EINVAL;
+    if(h->step_open)
+        return fail(h, B200OPT_ESTATE, "the previous bucketed step has no last bucket yet");
+    ++h->iter;
+    h->step_open = true;
+    return B200OPT_OK;
+}
+
+int b200opt_step_bucket(b200opt_t *h, size_t half_first, size_t half_count,
+                        size_t float_first, size_t float_count, float lr,
+                        float l2_lambda, float scale, void *stream, int last)
+{
+    if(!h)
+        return B200OPT_EINVAL;
+    if(!h->step_open)
+        return fail(h, B200OPT_ESTATE, "b200opt_step_begin has not been called");
+    if(half_first + half_count > h->n_half || float_first + float_count > h->n_float)
+        return fail(h, B200OPT_EINVAL, "bucket reaches beyond the flat buffer");
+    StepRange r;
+    r.whole = false;
+    r.h_first = half_first;
+    r.h_count = half_count;
+    r.f_first = float_first;
+    r.f_count = float_count;
+    const int rc = step_impl(h, lr, l2_lambda, scale, false, stream, r, false, last != 0);
+    if(rc == B200OPT_OK && last)
+        h->step_open = false;
+    return rc;
 }
 
 int b200opt_step_device_scale(b200opt_t *h, float lr, float l2_lambda,

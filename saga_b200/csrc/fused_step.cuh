@@ -77,15 +77,16 @@ struct HalfGroup {
     const uint16_t *G[kMaxRanks];  // gradient buffer of every rank
     float *m, *v, *c;  // local shard state; element i (global index) at [i - A]
     size_t o, s;       // shard start and length, elements
-    size_t A;          // o rounded down to a multiple of kVec
-    size_t ngroups;    // kVec-element groups covering [A, o+s)
+    size_t A;          // flat index of the element stored at [0] of m, v, c
+    size_t B;          // start of the first group: o rounded down to kVec
+    size_t ngroups;    // kVec-element groups covering [B, o+s)
 };
 
 struct FloatGroup {
     float *W[kMaxRanks];
     const float *G[kMaxRanks];
     float *m, *v;
-    size_t o, s, A, ngroups;
+    size_t o, s, A, B, ngroups;
 };
 
 struct StepParams {
@@ -96,6 +97,8 @@ struct StepParams {
     int barrier;      // 1: wait for peers inside the kernel
     int force_scalar; // 1: pointers are not 16-byte aligned, element-wise path
     int stages;       // staged kernel: depth of the shared-memory ring
+    int partial;      // 1: a bucket of a step that is not its last (no completion
+                      // protocol across ranks, flags keep accumulating)
     uint32_t epoch;
     unsigned long long timeout_ns;
     Ctrl *ctrl[kMaxRanks];  // control block of every rank (ctrl[rank] local)
@@ -610,7 +613,7 @@ __device__ __forceinline__ void float_group_pass(const StepParams &p,
     for(size_t base = (size_t)blockIdx.x * blockDim.x; base < ng;
         base += (size_t)gridDim.x * blockDim.x) {
         const size_t gid = base + tid;
-        const size_t idx0 = p.f.A + gid * kVec;
+        const size_t idx0 = p.f.B + gid * kVec;
         if(gid < ng) {
             if(idx0 >= lo && idx0 + kVec <= hi && !p.force_scalar) {
                 FloatLoads<NR> L;
@@ -666,6 +669,14 @@ __device__ __forceinline__ void step_finish(const StepParams &p, uint32_t fl,
     if(!*s_flag)
         return;
     __threadfence();
+
+    if(p.partial) {
+        // not the step's last bucket: later buckets of this stream follow in
+        // order, and the last one runs the completion protocol for all of them
+        if(tid == 0)
+            my->cta_done = 0;
+        return;
+    }
 
     const uint32_t mine =
         *reinterpret_cast<volatile uint32_t *>(&my->local_flags);
@@ -752,7 +763,7 @@ __global__ void __launch_bounds__(kThreads, MINB)
 #pragma unroll
             for(int k = 0; k < UNR; k++) {
                 const size_t gid = base + (size_t)k * kThreads + tid;
-                const size_t idx0 = p.h.A + gid * kVec;
+                const size_t idx0 = p.h.B + gid * kVec;
                 full[k] = gid < ng && idx0 >= lo && idx0 + kVec <= hi &&
                           !p.force_scalar;
                 if(full[k])
@@ -761,7 +772,7 @@ __global__ void __launch_bounds__(kThreads, MINB)
 #pragma unroll
             for(int k = 0; k < UNR; k++) {
                 const size_t gid = base + (size_t)k * kThreads + tid;
-                const size_t idx0 = p.h.A + gid * kVec;
+                const size_t idx0 = p.h.B + gid * kVec;
                 if(full[k])
                     half_compute_store<NR>(p, alpha, idx0, L[k], fl);
                 else if(gid < ng)

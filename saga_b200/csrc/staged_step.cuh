@@ -347,7 +347,7 @@ __global__ void __launch_bounds__(THREADS)
             const size_t ng = p.h.ngroups;
             for(size_t gid = (size_t)blockIdx.x * THREADS + tid; gid < ng;
                 gid += (size_t)gridDim.x * THREADS)
-                fl |= half_scalar<NR>(p, alpha, p.h.A + gid * kVec);
+                fl |= half_scalar<NR>(p, alpha, p.h.B + gid * kVec);
         } else if(blockIdx.x == 0 && p.h.s) {
             if(tid == 0 && lo != F0)
                 fl |= half_scalar<NR>(p, alpha, lo & ~(size_t)(kVec - 1));

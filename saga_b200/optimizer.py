@@ -179,6 +179,17 @@ class AdamGroup:
         """AdamF32::exec + AdamMixed::exec of this rank; asynchronous."""
         check(lib().b200opt_step(self._h, lr, l2_lambda, float(scale), C.c_void_p(stream)), self._h)
 
+    def step_begin(self):
+        """Opens a step that is issued bucket by bucket (exec_bucket)."""
+        check(lib().b200opt_step_begin(self._h), self._h)
+
+    def exec_bucket(self, half_range, float_range, lr, l2_lambda, scale, stream=0, last=False):
+        """Reduce + update + gather of one bucket: (first, count) per dtype group."""
+        hf, hc = half_range
+        ff, fc = float_range
+        check(lib().b200opt_step_bucket(self._h, hf, hc, ff, fc, lr, l2_lambda, float(scale),
+                                        C.c_void_p(stream), 1 if last else 0), self._h)
+
     def flags(self, stream=0):
         out = (C.c_uint32 * 3)()
         check(lib().b200opt_flags(self._h, C.c_void_p(stream), out), self._h)
