@@ -208,6 +208,9 @@ def main():
                     help="flat fp16 buffer of this many elements instead of the 160-tensor workload")
     ap.add_argument("--e2e-steps", type=int, default=0, help="default: min(steps, 50)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--with-ref-gpu", action="store_true",
+                    help="also time the reference's own compiled Adam kernel (oracle/_ref) as a "
+                         "GPU baseline beside the CPU one; off by default")
     ap.add_argument("--ctas-per-sm", type=int, default=0)
     ap.add_argument("--variant", type=int, default=-1)
     ap.add_argument("--stages", type=int, default=0)
@@ -317,10 +320,11 @@ def main():
         barrier()
         grp.set_option(capi.OPT_PATH, {"auto": capi.PATH_AUTO, "peer": capi.PATH_PEER}[args.path])
 
-    # ---- N = 1: the reference's own kernel (src/cuda/cuda_kernels.cu compiled
-    # unmodified for sm_100a, oracle/_ref) on buffers of the same size
+    # ---- N = 1, on request: a second baseline beside cpu_baseline -- the reference's own
+    # kernel (src/cuda/cuda_kernels.cu compiled unmodified for sm_100a, oracle/_ref) on
+    # buffers of the same size
     ref_gpu = None
-    if world == 1 and rank == 0:
+    if world == 1 and rank == 0 and args.with_ref_gpu:
         from oracle import oracle as orc
         if orc.ref_available():
             R = orc.ref()
