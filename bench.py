@@ -424,6 +424,8 @@ def main():
                 "bound": "nvlink", "achieved": nv, "peak": NVLINK_MEASURED_GBS, "unit": "GB/s",
                 "frac": nv / NVLINK_MEASURED_GBS, "frac_of_900_nominal": nv / NVLINK_NOMINAL_GBS,
                 "bytes_per_direction_per_launch": nv_bytes,
+                "note": "with several ranks the step is bound by NVLink, not HBM: this is the "
+                        "binding roofline, `roofline` above is the HBM side of the same launch",
             }
             if nccl_ms:
                 line["nccl_sequence"] = {

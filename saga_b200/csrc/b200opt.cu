@@ -154,13 +154,13 @@ void fill_groups(const b200opt *h, StepParams &p, const StepRange &r = StepRange
     p.h.c = h->ch;
     clip(h->oh, h->sh, r.whole, r.h_first, r.h_count, &p.h.o, &p.h.s);
     p.h.A = h->Ah;
-    p.h.B = p.h.o & ~(size_t)(kVec - 1);
+    p.h.B = p.h.o & ~(size_t)(kStateAlign - 1);
     p.h.ngroups = p.h.s ? (p.h.o + p.h.s - p.h.B + kVec - 1) / kVec : 0;
     p.f.m = h->mf;
     p.f.v = h->vf;
     clip(h->of, h->sf, r.whole, r.f_first, r.f_count, &p.f.o, &p.f.s);
     p.f.A = h->Af;
-    p.f.B = p.f.o & ~(size_t)(kVec - 1);
+    p.f.B = p.f.o & ~(size_t)(kStateAlign - 1);
     p.f.ngroups = p.f.s ? (p.f.o + p.f.s - p.f.B + kVec - 1) / kVec : 0;
 }
 

@@ -78,7 +78,8 @@ struct HalfGroup {
     float *m, *v, *c;  // local shard state; element i (global index) at [i - A]
     size_t o, s;       // shard start and length, elements
     size_t A;          // flat index of the element stored at [0] of m, v, c
-    size_t B;          // start of the first group: o rounded down to kVec
+    size_t B;          // index the group grid starts at: o rounded down so that a
+                       // warp's 512-byte access starts on a 512-byte boundary
     size_t ngroups;    // kVec-element groups covering [B, o+s)
 };
 
@@ -619,7 +620,7 @@ __device__ __forceinline__ void float_group_pass(const StepParams &p,
                 FloatLoads<NR> L;
                 float_load<NR>(p, idx0, L);
                 float_compute_store<NR>(p, idx0, L, fl);
-            } else {
+            } else if(idx0 + kVec > lo) {
                 fl |= float_scalar<NR>(p, idx0);
             }
         }
@@ -775,7 +776,7 @@ __global__ void __launch_bounds__(kThreads, MINB)
                 const size_t idx0 = p.h.B + gid * kVec;
                 if(full[k])
                     half_compute_store<NR>(p, alpha, idx0, L[k], fl);
-                else if(gid < ng)
+                else if(gid < ng && idx0 + kVec > lo)
                     fl |= half_scalar<NR>(p, alpha, idx0);
             }
         }

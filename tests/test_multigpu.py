@@ -118,7 +118,7 @@ def test_mismatched_sizes_are_refused_at_wiring():
 @pytest.mark.parametrize("path", ["peer", "nccl"])
 def test_one_process_per_gpu_over_cuda_ipc(tmp_path, path):
     """torchrun-style launch: peers attached through b200opt_ipc_export/attach."""
-    nproc = 2
+    nproc = _ngpu() if _ngpu() in (4, 8) else 2
     out = tmp_path / f"mp_{path}.json"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node",
            str(nproc), "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
