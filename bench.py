@@ -196,6 +196,61 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+# ----------------------------------------------- N-rank kernel on one GPU (ncu aid)
+
+def run_serial_ranks(args):
+    """All N ranks live on GPU 0 and are stepped in turn, so the N-rank instance
+    of the step kernel can be captured by ncu (which never wraps a multi-rank
+    command here).  Peer loads and stores hit local HBM: the line reports the
+    SM-side cost of one rank's launch, not an NVLink figure, and is not a
+    benchmark value."""
+    import torch
+    from saga_b200 import AdamGroup, capi
+    N = args.serial_ranks
+    sizes, lay = workload()
+    n = args.params or lay.total
+    dev = torch.device("cuda", 0)
+    groups = AdamGroup.create_group([0] * N, n, 0)
+    stream = torch.cuda.current_stream(dev)
+    sp = stream.cuda_stream
+    gen = torch.Generator(device=dev).manual_seed(0x5A6A)
+    w0 = (torch.randn(n, device=dev, generator=gen) * 0.02).half()
+    for r, g in enumerate(groups):
+        if args.variant >= 0:
+            g.set_option(capi.OPT_KERNEL_VARIANT, args.variant)
+        if args.ctas_per_sm:
+            g.set_option(capi.OPT_CTAS_PER_SM, args.ctas_per_sm)
+        w, gr = g.buffers(capi.HALF)
+        w.copy_(w0)
+        gr.copy_((torch.randn(n, device=dev, generator=gen) * (1e-3 * SCALE0)).half())
+        g.init_master(sp)
+    torch.cuda.synchronize(dev)
+
+    def one_round():
+        for g in groups:
+            g.exec(LR, L2, SCALE0, sp)
+
+    for _ in range(max(args.warmup, 3)):
+        one_round()
+    torch.cuda.synchronize(dev)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(args.steps):
+        one_round()
+    b.record(stream)
+    torch.cuda.synchronize(dev)
+    flags = groups[0].flags(sp)
+    us = a.elapsed_time(b) / (args.steps * N) * 1e3
+    # one rank's launch: N gradient shards in, m/v/master in and out, N weight shards out
+    alg = (4 * n + 24 * n / N) / 1.0
+    print(json.dumps({
+        "mode": "serial-ranks (profiling aid, not a benchmark value)", "ranks_on_one_gpu": N,
+        "n_params": n, "us_per_rank_launch": us, "local_hbm_gbs": alg / (us * 1e-6) / 1e9,
+        "algorithmic_bytes_per_launch": alg, "flags": list(flags)}), flush=True)
+    for g in groups:
+        g.destroy()
+
+
 # ------------------------------------------------------------------- our arm
 
 def main():
@@ -216,9 +271,14 @@ def main():
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--grid", type=int, default=0)
     ap.add_argument("--path", default="auto", choices=["auto", "peer", "nccl"])
+    ap.add_argument("--serial-ranks", type=int, default=0,
+                    help="profiling aid: N ranks on ONE GPU, stepped one after the other "
+                         "(no cross-GPU waits); times the N-rank kernel against local HBM only")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.serial_ranks:
+        return run_serial_ranks(args)
     args.warmup = max(args.warmup, 3)
 
     import torch
