@@ -270,7 +270,7 @@ def main():
     ap.add_argument("--variant", type=int, default=-1)
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--grid", type=int, default=0)
-    ap.add_argument("--path", default="auto", choices=["auto", "peer", "nccl"])
+    ap.add_argument("--path", default="auto", choices=["auto", "peer", "push", "nccl"])
     ap.add_argument("--serial-ranks", type=int, default=0,
                     help="profiling aid: N ranks on ONE GPU, stepped one after the other "
                          "(no cross-GPU waits); times the N-rank kernel against local HBM only")
@@ -312,7 +312,7 @@ def main():
         from saga_b200 import launch
         launch.wire_process_group(grp, with_nccl=True)
         grp.set_option(capi.OPT_PATH, {"auto": capi.PATH_AUTO, "peer": capi.PATH_PEER,
-                                       "nccl": capi.PATH_NCCL}[args.path])
+                                       "push": capi.PATH_PUSH, "nccl": capi.PATH_NCCL}[args.path])
     if args.ctas_per_sm:
         grp.set_option(capi.OPT_CTAS_PER_SM, args.ctas_per_sm)
     if args.variant >= 0:
@@ -378,7 +378,8 @@ def main():
         nccl_ms = timed_steps(k) / k
         grp.flags(sp)
         barrier()
-        grp.set_option(capi.OPT_PATH, {"auto": capi.PATH_AUTO, "peer": capi.PATH_PEER}[args.path])
+        grp.set_option(capi.OPT_PATH, {"auto": capi.PATH_AUTO, "peer": capi.PATH_PEER,
+                                       "push": capi.PATH_PUSH}[args.path])
 
     # ---- N = 1, on request: a second baseline beside cpu_baseline -- the reference's own
     # kernel (src/cuda/cuda_kernels.cu compiled unmodified for sm_100a, oracle/_ref) on

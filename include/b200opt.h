@@ -57,6 +57,8 @@ extern "C" {
 #define B200OPT_PATH_AUTO 0 /* peer kernel, NCCL below the measured crossover */
 #define B200OPT_PATH_PEER 1 /* fused peer-memory kernel always */
 #define B200OPT_PATH_NCCL 2 /* ncclReduceScatter + Adam kernel + ncclAllGather */
+#define B200OPT_PATH_PUSH 3 /* ranks store their gradient contributions into the owners' staging
+                               slots, then the fused kernel sums locally: stores only on NVLink */
 
 /* options */
 #define B200OPT_OPT_TIMEOUT_MS 1    /* limit of every cross-GPU wait (default 10000) */

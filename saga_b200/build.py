@@ -13,7 +13,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200opt.so")
 
 SOURCES = ["b200opt.cu", "host_logic.cpp", "nccl_path.cpp"]
-HEADERS = ["fused_step.cuh", "staged_step.cuh", "warp_ring_step.cuh", "nccl_path.h", os.path.join("..", "..", "include", "b200opt.h")]
+HEADERS = ["fused_step.cuh", "staged_step.cuh", "warp_ring_step.cuh", "push_grads.cuh", "nccl_path.h", os.path.join("..", "..", "include", "b200opt.h")]
 
 
 def _nvcc():

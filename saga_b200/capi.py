@@ -13,7 +13,7 @@ OK, EINVAL, ECUDA, ENOMEM, ETIMEOUT, ESTATE, EUNSUPPORTED, ETOOBIG = 0, -1, -2, 
 STATIC_MAX_ELEMS = 1 << 30
 HALF, FLOAT = 0, 1
 POLICY_REFERENCE, POLICY_INTERVAL = 0, 1
-PATH_AUTO, PATH_PEER, PATH_NCCL = 0, 1, 2
+PATH_AUTO, PATH_PEER, PATH_NCCL, PATH_PUSH = 0, 1, 2, 3
 OPT_TIMEOUT_MS, OPT_PATH, OPT_CTAS_PER_SM, OPT_KERNEL_VARIANT, OPT_NCCL_CROSSOVER = 1, 2, 3, 4, 5
 OPT_STAGES, OPT_GRID = 6, 7
 MAX_RANKS = 8

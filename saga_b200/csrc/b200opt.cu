@@ -16,6 +16,7 @@
 #include "fused_step.cuh"
 #include "staged_step.cuh"
 #include "warp_ring_step.cuh"
+#include "push_grads.cuh"
 #include "nccl_path.h"
 
 using namespace b200;
@@ -44,6 +45,9 @@ struct b200opt {
     char *arena = nullptr;
     size_t arena_bytes = 0;
     size_t off_wh = 0, off_gh = 0, off_wf = 0, off_gf = 0;
+    // staging of the push path: nranks slots per dtype group, slot q receives
+    // rank q's contribution to this rank's shard
+    size_t off_sh = 0, off_sf = 0, slot_h_bytes = 0, slot_f_bytes = 0;
     char *peer_arena[kMaxRanks] = {};
     bool peer_is_ipc[kMaxRanks] = {};
     int peers_attached = 0;
@@ -424,7 +428,13 @@ int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
     h->off_gh = h->off_wh + round_up(n_half * 2, 256);
     h->off_wf = h->off_gh + round_up(n_half * 2, 256);
     h->off_gf = h->off_wf + round_up(n_float * 4, 256);
-    h->arena_bytes = h->off_gf + round_up(n_float * 4, 256);
+    h->off_sh = h->off_gf + round_up(n_float * 4, 256);
+    if(nranks > 1) {
+        h->slot_h_bytes = h->sh ? round_up((h->sh + kStateAlign + 2 * kVec) * 2, 256) : 0;
+        h->slot_f_bytes = h->sf ? round_up((h->sf + kStateAlign + 2 * kVec) * 4, 256) : 0;
+    }
+    h->off_sf = h->off_sh + h->slot_h_bytes * nranks;
+    h->arena_bytes = h->off_sf + h->slot_f_bytes * nranks;
 
     DeviceGuard guard(device);
     int rc = B200OPT_OK;
@@ -775,6 +785,44 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
     fill_groups(h, p, range);
     p.partial = last ? 0 : 1;
     p.barrier = (h->nranks > 1 && !h->serial) ? 1 : 0;
+    if(h->path == B200OPT_PATH_PUSH && h->nranks > 1) {
+        if(h->serial || !range.whole)
+            return fail(h, B200OPT_EUNSUPPORTED,
+                        "the push path needs one GPU per rank and whole steps");
+        // 1. write this rank's contributions into the owners' staging slots
+        PushParams pp;
+        memset(&pp, 0, sizeof(pp));
+        pp.Gh = arena_ptr<uint16_t>(h->arena, h->off_gh);
+        pp.Gf = arena_ptr<float>(h->arena, h->off_gf);
+        pp.sh = h->sh;
+        pp.sf = h->sf;
+        pp.rank = h->rank;
+        pp.nranks = h->nranks;
+        pp.epoch = p.epoch;
+        for(int q = 0; q < h->nranks; q++) {
+            char *base = h->peer_arena[q];
+            pp.ctrl[q] = arena_ptr<Ctrl>(base, 0);
+            const size_t Aq = (h->sh * q) & ~(size_t)(kStateAlign - 1);
+            const size_t Afq = (h->sf * q) & ~(size_t)(kStateAlign - 1);
+            pp.Sh[q] = arena_ptr<uint16_t>(base, h->off_sh + h->slot_h_bytes * h->rank) - Aq;
+            pp.Sf[q] = arena_ptr<float>(base, h->off_sf + h->slot_f_bytes * h->rank) - Afq;
+        }
+        const size_t bytes = (h->sh * 2 + h->sf * 4) * (size_t)(h->nranks - 1);
+        const size_t per_cta = (size_t)kPushThreads * kPushUnroll * 16;
+        const int pgrid = (int)std::min<size_t>(std::max<size_t>(bytes / per_cta, 1),
+                                                (size_t)h->num_sms * 4);
+        push_grads_kernel<<<pgrid, kPushThreads, 0, st>>>(pp);
+        CK(h, cudaGetLastError());
+        h->launches++;
+        // 2. the step kernel sums its own shard with the staged ones: local loads
+        for(int q = 0; q < h->nranks; q++) {
+            if(q == h->rank)
+                continue;
+            p.h.G[q] = arena_ptr<uint16_t>(h->arena, h->off_sh + h->slot_h_bytes * q) - h->Ah;
+            p.f.G[q] = arena_ptr<float>(h->arena, h->off_sf + h->slot_f_bytes * q) - h->Af;
+        }
+        p.no_announce = 1;
+    }
     CK(h, launch_step(p, h->nranks, h->num_sms, tuning_of(h), st));
     h->launches++;
     return B200OPT_OK;
@@ -1229,7 +1277,7 @@ int b200opt_set_option(b200opt_t *h, int option, long value)
         h->timeout_ms = value;
         return B200OPT_OK;
     case B200OPT_OPT_PATH:
-        if(value < B200OPT_PATH_AUTO || value > B200OPT_PATH_NCCL)
+        if(value < B200OPT_PATH_AUTO || value > B200OPT_PATH_PUSH)
             return B200OPT_EINVAL;
         h->path = value;
         return B200OPT_OK;

@@ -51,7 +51,7 @@ struct alignas(128) Ctrl {
     uint32_t cta_done;         // CTAs of the running launch that finished
     uint32_t local_flags;      // OR of this rank's flag bits
     uint32_t status;           // sticky B200OPT_E* (as positive number) or 0
-    uint32_t pad0;
+    uint32_t push_done;        // CTAs of the running gradient-push launch that finished
     uint32_t coll_flags[4];    // NCCL path: {range, inf, nan} to be all-reduced
     // device-resident loss scale (optional): updated by the last CTA of a step
     float scale;               // current loss scale
@@ -98,6 +98,8 @@ struct StepParams {
     int barrier;      // 1: wait for peers inside the kernel
     int force_scalar; // 1: pointers are not 16-byte aligned, element-wise path
     int stages;       // staged kernel: depth of the shared-memory ring
+    int no_announce;  // 1: the gradient-push kernel has already told the peers that
+                      // this rank's contributions are in place
     int partial;      // 1: a bucket of a step that is not its last (no completion
                       // protocol across ranks, flags keep accumulating)
     uint32_t epoch;
@@ -586,7 +588,7 @@ __device__ __forceinline__ int step_begin(const StepParams &p)
         return 0;
     const int tid = threadIdx.x;
     Ctrl *const my = p.ctrl[p.rank];
-    if(blockIdx.x == 0 && tid < NR)
+    if(blockIdx.x == 0 && tid < NR && !p.no_announce)
         st_release_sys(&p.ctrl[tid]->ready[p.rank], p.epoch);
     int bad = 0;
     if(tid < NR) {

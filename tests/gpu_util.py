@@ -24,7 +24,7 @@ def stream_ptr(device=0):
 class Program:
     """N ranks of the CUDA path with the weights/gradients API the tests need."""
 
-    def __init__(self, nranks, n_half, n_float=0, devices=None, variant=None):
+    def __init__(self, nranks, n_half, n_float=0, devices=None, variant=None, path=None):
         devices = devices or [0] * nranks
         self.N = nranks
         self.devices = devices
@@ -34,6 +34,8 @@ class Program:
         for g in self.groups:
             if variant is not None:
                 g.set_option(capi.OPT_KERNEL_VARIANT, variant)
+            if path is not None:
+                g.set_option(capi.OPT_PATH, path)
             w, gr = g.buffers(capi.HALF)
             self.Wh.append(w)
             self.Gh.append(gr)

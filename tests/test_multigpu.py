@@ -40,13 +40,33 @@ def test_two_gpus_one_process_matches_oracle(oracle, variant):
                         inject_every=3, variant=variant, devices=[0, 1])
 
 
-def test_all_gpus_one_process_matches_oracle(oracle):
+@pytest.mark.parametrize("variant", [1, 4])
+def test_two_gpus_push_path_matches_oracle(oracle, variant):
+    """Gradient contributions stored into the owners' staging slots, then summed locally."""
+    for n_half, n_float in ((16, 16), (8208, 528), (2048 * 7 * 2 + 80, 0)):
+        _run_trajectory(oracle, 2, n_half, n_float, 6, 1e-2, 0.01, 64.0, seed=83,
+                        inject_every=3, variant=variant, devices=[0, 1], path=capi.PATH_PUSH)
+
+
+def test_push_path_is_refused_in_serial_mode(oracle):
+    prog = Program(2, 4096, path=capi.PATH_PUSH)
+    try:
+        prog.set_weights([synth.weights_half(4096, seed=1)] * 2)
+        with pytest.raises(B200OptError) as err:
+            prog.groups[0].exec(1e-3, 0.0, 1.0, stream_ptr(0))
+        assert err.value.status == capi.EUNSUPPORTED
+    finally:
+        prog.close()
+
+
+@pytest.mark.parametrize("path", [capi.PATH_PEER, capi.PATH_PUSH])
+def test_all_gpus_one_process_matches_oracle(oracle, path):
     n = _ngpu()
     if n < 4:
         pytest.skip("needs >= 4 GPUs")
     n = 8 if n >= 8 else 4
     _run_trajectory(oracle, n, 2048 * 5 * n + 16, 528, 6, 1e-2, 0.01, 64.0, seed=82,
-                    inject_every=3, devices=list(range(n)))
+                    inject_every=3, devices=list(range(n)), path=path)
 
 
 def test_driver_in_sagas_threading_model():
@@ -115,7 +135,7 @@ def test_mismatched_sizes_are_refused_at_wiring():
         b.destroy()
 
 
-@pytest.mark.parametrize("path", ["peer", "nccl"])
+@pytest.mark.parametrize("path", ["peer", "push", "nccl"])
 def test_one_process_per_gpu_over_cuda_ipc(tmp_path, path):
     """torchrun-style launch: peers attached through b200opt_ipc_export/attach."""
     nproc = _ngpu() if _ngpu() in (4, 8) else 2
@@ -128,5 +148,5 @@ def test_one_process_per_gpu_over_cuda_ipc(tmp_path, path):
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-6000:]
     got = json.loads(out.read_text())
     assert got["ok"] and len(got["ranks"]) == nproc
-    if path == "peer":
+    if path in ("peer", "push"):
         assert all(r["worst_rel_err"] <= 1e-5 and r["w_ulp_diff_max"] <= 1 for r in got["ranks"])

@@ -167,10 +167,11 @@ VARIANTS = [1, 6, 2, 3, 4, 5, 7, 8, 9, 10]  # direct loads, CTA-wide rings, per-
 
 
 def _run_trajectory(oracle, nranks, n_half, n_float, steps, lr, l2, scale0, seed,
-                    inject_every=0, check_every=1, tol_final=TOL_100, variant=None, devices=None):
+                    inject_every=0, check_every=1, tol_final=TOL_100, variant=None, devices=None,
+                    path=None):
     W0 = synth.weights_half(n_half, seed=seed) if n_half else None
     Wf0 = synth.weights_float(n_float, seed=seed) if n_float else None
-    prog = Program(nranks, n_half, n_float, variant=variant, devices=devices)
+    prog = Program(nranks, n_half, n_float, variant=variant, devices=devices, path=path)
     prog.set_weights([W0] * nranks if n_half else None, [Wf0] * nranks if n_float else None)
     ost = oracle.MultiRankState(nranks, [W0] * nranks if n_half else None,
                                 [Wf0] * nranks if n_float else None)
