@@ -261,6 +261,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--params", type=int, default=0,
                     help="flat fp16 buffer of this many elements instead of the 160-tensor workload")
+    ap.add_argument("--fp32-group", action="store_true",
+                    help="put the parameters in the fp32 group (the reference's AdamF32 path: "
+                         "fp32 weights and gradients, no master copy) instead of the fp16 group")
     ap.add_argument("--e2e-steps", type=int, default=0, help="default: min(steps, 50)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--with-ref-gpu", action="store_true",
@@ -307,7 +310,10 @@ def main():
         n = lay.total
         wl = "config2: 25.6M fp16 params in 160 tensors, 1 optimizer step"
 
-    grp = AdamGroup.create(rank, world, local, n, 0)
+    f32 = args.fp32_group
+    if f32:
+        wl = wl.replace("fp16", "fp32") + " (fp32 group)"
+    grp = AdamGroup.create(rank, world, local, 0 if f32 else n, n if f32 else 0)
     if world > 1:
         from saga_b200 import launch
         launch.wire_process_group(grp, with_nccl=True)
@@ -324,14 +330,15 @@ def main():
 
     stream = torch.cuda.current_stream(dev)
     sp = stream.cuda_stream
-    w, g = grp.buffers(capi.HALF)
+    w, g = grp.buffers(capi.FLOAT if f32 else capi.HALF)
     gen = torch.Generator(device=dev).manual_seed(0x5A6A)          # same weights on every rank
-    w.copy_((torch.randn(n, device=dev, generator=gen) * 0.02).half())
+    w.copy_((torch.randn(n, device=dev, generator=gen) * 0.02).to(w.dtype))
     gen_g = torch.Generator(device=dev).manual_seed(0x5A6A + 1 + rank)  # own gradients per rank
-    g.copy_((torch.randn(n, device=dev, generator=gen_g) * (1e-3 * SCALE0)).half())
+    g.copy_((torch.randn(n, device=dev, generator=gen_g) * (1e-3 * SCALE0)).to(g.dtype))
     grp.init_master(sp)
-    host_g = torch.empty(n, dtype=torch.float16).pin_memory()
+    host_g = torch.empty(n, dtype=g.dtype).pin_memory()
     host_g.copy_(g)
+    host_ptrs = (0, host_g.data_ptr()) if f32 else (host_g.data_ptr(), 0)
     torch.cuda.synchronize(dev)
 
     def barrier():
@@ -421,11 +428,11 @@ def main():
     # updates the loss scale on the host (what Saga's step tail does)
     e2e_steps = args.e2e_steps or min(args.steps, 50)
     for _ in range(3):
-        grp.step_host(host_g.data_ptr(), 0, LR, L2, scaler.scale, sp)
+        grp.step_host(host_ptrs[0], host_ptrs[1], LR, L2, scaler.scale, sp)
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        fl = grp.step_host(host_g.data_ptr(), 0, LR, L2, scaler.scale, sp)
+        fl = grp.step_host(host_ptrs[0], host_ptrs[1], LR, L2, scaler.scale, sp)
         scaler.update(fl)
     torch.cuda.synchronize(dev)
     e2e_s = time.perf_counter() - t0
@@ -444,6 +451,8 @@ def main():
         # shard copy (2n in total over self+peers), read+write m/v/master of the
         # shard (24n/N), write the fp16 weights of the whole buffer (2n)
         alg_bytes = 4 * n + 24 * n / world
+        if f32:  # gradients 4 B read per rank copy, weights 4 B written per rank copy, w/m/v of the shard
+            alg_bytes = 8 * n + 20 * n / world
         achieved = alg_bytes / (per_step_ms * 1e-3) / 1e9
         line = {
             "metric": "fused grad-reduce+Adam params/sec",
@@ -465,13 +474,13 @@ def main():
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                 "frac": achieved / hbm_peak,
-                "traffic": NCU_TRAFFIC_N1_BYTES if (world == 1 and not args.params) else None,
+                "traffic": NCU_TRAFFIC_N1_BYTES if (world == 1 and not args.params and not f32) else None,
                 "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": alg_bytes,
                 "frac_of_8000_nominal": achieved / 8000.0,
             },
             "e2e": {
                 "value": world * n * e2e_steps / e2e_s, "unit": "params/s",
-                "h2d_bytes_per_step": 2 * n, "d2h_bytes_per_step": 32,
+                "h2d_bytes_per_step": (4 if f32 else 2) * n, "d2h_bytes_per_step": 32,
                 "ms_per_step": e2e_s / e2e_steps * 1e3, "steps": e2e_steps,
             },
             "gpu_launches": int(launches),
@@ -479,7 +488,7 @@ def main():
             "flags_last_step": list(flags),
         }
         if world > 1:
-            nv_bytes = 4 * n * (world - 1) / world
+            nv_bytes = (8 if f32 else 4) * n * (world - 1) / world
             nv = nv_bytes / (per_step_ms * 1e-3) / 1e9
             line["roofline_nvlink"] = {
                 "bound": "nvlink", "achieved": nv, "peak": NVLINK_MEASURED_GBS, "unit": "GB/s",
