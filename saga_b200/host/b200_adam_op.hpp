@@ -26,6 +26,7 @@
 #pragma once
 
 #include <condition_variable>
+#include <functional>
 #include <map>
 #include <mutex>
 #include <stdexcept>
@@ -95,7 +96,12 @@ struct B200Adam : public CudaOperation {
     {
     }
 
-    ~B200Adam() { b200opt_destroy(m_handle); }
+    ~B200Adam()
+    {
+        if(m_on_destroy)
+            m_on_destroy();  // lets the owner forget the handle first
+        b200opt_destroy(m_handle);
+    }
 
     // AdamF32::exec + AdamMixed::exec (src/cuda/cuda_optimizer.cpp:76-113,
     // 148-186): iteration counter, bias corrections, 1/scale, reduce-scatter,
@@ -130,6 +136,7 @@ struct B200Adam : public CudaOperation {
     CudaOpArgs listOutputs() const override { return m_outputs; }
 
     b200opt_t *m_handle;
+    std::function<void()> m_on_destroy;
     CudaOpArgs m_inputs;
     CudaOpArgs m_outputs;
     const std::shared_ptr<CudaContext> m_ctx;
