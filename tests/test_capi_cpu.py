@@ -87,3 +87,15 @@ def test_argument_checks_without_a_gpu(built_library):
     fl = (C.c_uint32 * 3)(0, 0, 0)
     assert L.b200opt_policy_update(C.byref(s), fl, 7, None, 0) == capi.EINVAL
     assert L.b200opt_policy_update(C.byref(s), fl, capi.POLICY_INTERVAL, None, 2000) == capi.EINVAL
+
+
+def test_header_is_plain_c(tmp_path):
+    """include/b200opt.h must compile as C99 on its own: it is what foreign hosts bind."""
+    import subprocess
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "b200opt.h"\n'
+                   'int main(void) { b200opt_t *h = 0; (void)h; return B200OPT_MAX_RANKS == 8 ? 0 : 1; }\n')
+    res = subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-fsyntax-only",
+                          "-I", os.path.join(ROOT, "include"), str(src)],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
