@@ -67,6 +67,7 @@ extern "C" {
 #define B200OPT_OPT_KERNEL_VARIANT 4 /* 0 = default; 1,6 = direct 16-byte loads; 2..5 = bulk-copy staging through shared memory; 7..10 = the same with one ring per warp */
 #define B200OPT_OPT_NCCL_CROSSOVER 5 /* AUTO uses NCCL when n_half is below this many elements */
 #define B200OPT_OPT_STAGES 6        /* depth of the shared-memory ring of the staged kernel (tuning) */
+#define B200OPT_OPT_L2_HINT 8       /* staged kernel: 1 loads, 2 stores, 3 both carry an L2 evict-first hint (tuning) */
 #define B200OPT_OPT_GRID 7          /* number of CTAs of the step kernel, overrides CTAS_PER_SM (tuning) */
 
 typedef struct b200opt b200opt_t;

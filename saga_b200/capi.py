@@ -15,7 +15,7 @@ HALF, FLOAT = 0, 1
 POLICY_REFERENCE, POLICY_INTERVAL = 0, 1
 PATH_AUTO, PATH_PEER, PATH_NCCL, PATH_PUSH = 0, 1, 2, 3
 OPT_TIMEOUT_MS, OPT_PATH, OPT_CTAS_PER_SM, OPT_KERNEL_VARIANT, OPT_NCCL_CROSSOVER = 1, 2, 3, 4, 5
-OPT_STAGES, OPT_GRID = 6, 7
+OPT_STAGES, OPT_GRID, OPT_L2_HINT = 6, 7, 8
 MAX_RANKS = 8
 IPC_HANDLE_BYTES = 64
 NCCL_ID_BYTES = 128

@@ -70,6 +70,7 @@ struct b200opt {
     long variant = 0;
     long stages = 0;
     long grid = 0;
+    long l2_hint = 0;
     long nccl_crossover = 0;
     uint64_t launches = 0;
     NcclPath *nccl = nullptr;
@@ -181,6 +182,7 @@ struct LaunchTuning {
     long variant = 0;
     long stages = 0;
     long grid = 0;
+    long l2_hint = 0;
 };
 
 template <int NR, int VEC, int THREADS>
@@ -221,6 +223,7 @@ cudaError_t launch_staged(StepParams p, int num_sms, const LaunchTuning &t,
     const size_t cap = t.grid > 0 ? (size_t)t.grid : (size_t)num_sms * cps;
     const int grid = (int)std::min<size_t>(want, cap);
     p.stages = stages;
+    p.l2_hint = (int)t.l2_hint;
     kern<<<grid, THREADS, smem, st>>>(p);
     return cudaGetLastError();
 }
@@ -358,6 +361,7 @@ LaunchTuning tuning_of(const b200opt *h)
     t.variant = h->variant;
     t.stages = h->stages;
     t.grid = h->grid;
+    t.l2_hint = h->l2_hint;
     return t;
 }
 
@@ -1306,6 +1310,11 @@ int b200opt_set_option(b200opt_t *h, int option, long value)
             return B200OPT_EINVAL;
         h->grid = value;
         return B200OPT_OK;
+    case B200OPT_OPT_L2_HINT:
+        if(value < 0 || value > 3)
+            return B200OPT_EINVAL;
+        h->l2_hint = value;
+        return B200OPT_OK;
     }
     return B200OPT_EINVAL;
 }
@@ -1322,6 +1331,7 @@ int b200opt_get_option(const b200opt_t *h, int option, long *value)
     case B200OPT_OPT_NCCL_CROSSOVER: *value = h->nccl_crossover; return B200OPT_OK;
     case B200OPT_OPT_STAGES: *value = h->stages; return B200OPT_OK;
     case B200OPT_OPT_GRID: *value = h->grid; return B200OPT_OK;
+    case B200OPT_OPT_L2_HINT: *value = h->l2_hint; return B200OPT_OK;
     }
     return B200OPT_EINVAL;
 }

@@ -98,6 +98,7 @@ struct StepParams {
     int barrier;      // 1: wait for peers inside the kernel
     int force_scalar; // 1: pointers are not 16-byte aligned, element-wise path
     int stages;       // staged kernel: depth of the shared-memory ring
+    int l2_hint;      // staged kernel: bit 0 loads, bit 1 stores carry an L2 evict-first hint
     int no_announce;  // 1: the gradient-push kernel has already told the peers that
                       // this rank's contributions are in place
     int partial;      // 1: a bucket of a step that is not its last (no completion
