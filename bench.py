@@ -274,6 +274,9 @@ def main():
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--grid", type=int, default=0)
     ap.add_argument("--path", default="auto", choices=["auto", "peer", "push", "nccl"])
+    ap.add_argument("--with-allreduce-baseline", action="store_true",
+                    help="N > 1: also time NCCL all-reduce of the whole fp16 gradient buffer followed "
+                         "by the one-GPU Adam kernel over all parameters on every rank")
     ap.add_argument("--serial-ranks", type=int, default=0,
                     help="profiling aid: N ranks on ONE GPU, stepped one after the other "
                          "(no cross-GPU waits); times the N-rank kernel against local HBM only")
@@ -388,6 +391,38 @@ def main():
         grp.set_option(capi.OPT_PATH, {"auto": capi.PATH_AUTO, "peer": capi.PATH_PEER,
                                        "push": capi.PATH_PUSH}[args.path])
 
+    # ---- N > 1, on request: the other classic arrangement -- all-reduce the whole
+    # gradient buffer (NCCL, fp16), then every rank updates ALL parameters with the
+    # one-GPU kernel (unsharded optimizer state)
+    allreduce_ms = None
+    if world > 1 and args.with_allreduce_baseline and not f32:
+        from saga_b200 import optimizer as opt_mod
+        from saga_b200 import bias_corrections
+        aw, ag = w.clone(), g.clone()
+        am, av = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        ac = aw.float()
+        aux = torch.zeros(4, dtype=torch.int32, device=dev)
+        b1t, b2t = bias_corrections(1)
+
+        def ar_step():
+            dist.all_reduce(ag, op=dist.ReduceOp.AVG)   # AVG keeps the values bounded over many steps
+            opt_mod.adam_mixed(n, 1.0 / SCALE0, aw.data_ptr(), ag.data_ptr(), am.data_ptr(),
+                               av.data_ptr(), ac.data_ptr(), float(b1t), float(b2t), LR, L2,
+                               aux.data_ptr(), sp)
+        for _ in range(5):
+            ar_step()
+        barrier()
+        k = min(args.steps, 200)
+        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ea.record(stream)
+        for _ in range(k):
+            ar_step()
+        eb.record(stream)
+        torch.cuda.synchronize(dev)
+        allreduce_ms = ea.elapsed_time(eb) / k
+        barrier()
+        del aw, ag, am, av, ac
+
     # ---- N = 1, on request: a second baseline beside cpu_baseline -- the reference's own
     # kernel (src/cuda/cuda_kernels.cu compiled unmodified for sm_100a, oracle/_ref) on
     # buffers of the same size
@@ -440,9 +475,11 @@ def main():
     clocks = sampler.stop() if sampler else None
 
     if world > 1:
-        t = torch.tensor([ms, e2e_s, nccl_ms or 0.0], dtype=torch.float64, device=dev)
+        t = torch.tensor([ms, e2e_s, nccl_ms or 0.0, allreduce_ms or 0.0], dtype=torch.float64,
+                         device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_s, nccl_ms = float(t[0]), float(t[1]), float(t[2]) or None
+        allreduce_ms = float(t[3]) or None
 
     if rank == 0:
         per_step_ms = ms / args.steps
@@ -502,6 +539,11 @@ def main():
                     "what": "ncclReduceScatter + Adam kernel on the shard + ncclAllGather + "
                             "3-word ncclAllReduce, the reference's call sequence, same buffers",
                     "ms_per_step": nccl_ms, "speedup_of_fused_kernel": nccl_ms / per_step_ms}
+        if allreduce_ms:
+            line["allreduce_sequence"] = {
+                "what": "NCCL all-reduce of the whole fp16 gradient buffer + one-GPU Adam kernel over "
+                        "all parameters on every rank (unsharded state)",
+                "ms_per_step": allreduce_ms, "speedup_of_fused_kernel": allreduce_ms / per_step_ms}
         if ref_gpu:
             ref_gpu["speedup_of_fused_kernel"] = ref_gpu["ms_per_step"] / per_step_ms
             line["ref_gpu"] = ref_gpu
