@@ -710,6 +710,27 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
                     "an earlier step timed out; the handle is unusable");
     if(h->peers_attached != h->nranks)
         return fail(h, B200OPT_ESTATE, "not every peer rank is attached");
+    // everything that can refuse the call is checked before any counter moves
+    const bool use_nccl =
+        h->nranks > 1 && !h->serial &&
+        (h->path == B200OPT_PATH_NCCL ||
+         (h->path == B200OPT_PATH_AUTO && h->nccl &&
+          (long)h->n_half < h->nccl_crossover));
+    if(use_nccl) {
+        if(!range.whole)
+            return fail(h, B200OPT_EUNSUPPORTED,
+                        "bucketed steps need the peer-kernel path");
+        if(device_scale)
+            return fail(h, B200OPT_EUNSUPPORTED,
+                        "the device-resident loss scale needs the peer-kernel path");
+        if(!h->nccl)
+            return fail(h, B200OPT_ESTATE,
+                        "NCCL path selected but b200opt_nccl_init was not called");
+    } else if(h->path == B200OPT_PATH_PUSH && h->nranks > 1 &&
+              (h->serial || !range.whole)) {
+        return fail(h, B200OPT_EUNSUPPORTED,
+                    "the push path needs one GPU per rank and whole steps");
+    }
     DeviceGuard guard(h->device);
     cudaStream_t st = (cudaStream_t)stream;
 
@@ -731,21 +752,7 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
     p.timeout_ns = (unsigned long long)h->timeout_ms * 1000000ull;
     p.host = h->host_dev;
 
-    const bool use_nccl =
-        h->nranks > 1 && !h->serial &&
-        (h->path == B200OPT_PATH_NCCL ||
-         (h->path == B200OPT_PATH_AUTO && h->nccl &&
-          (long)h->n_half < h->nccl_crossover));
     if(use_nccl) {
-        if(!range.whole)
-            return fail(h, B200OPT_EUNSUPPORTED,
-                        "bucketed steps need the peer-kernel path");
-        if(device_scale)
-            return fail(h, B200OPT_EUNSUPPORTED,
-                        "the device-resident loss scale needs the peer-kernel path");
-        if(!h->nccl)
-            return fail(h, B200OPT_ESTATE,
-                        "NCCL path selected but b200opt_nccl_init was not called");
         // reduce-scatter in place, Adam on the local shard, all-gather, flag sum
         std::string err;
         uint16_t *wh = arena_ptr<uint16_t>(h->arena, h->off_wh);
@@ -790,9 +797,6 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
     p.partial = last ? 0 : 1;
     p.barrier = (h->nranks > 1 && !h->serial) ? 1 : 0;
     if(h->path == B200OPT_PATH_PUSH && h->nranks > 1) {
-        if(h->serial || !range.whole)
-            return fail(h, B200OPT_EUNSUPPORTED,
-                        "the push path needs one GPU per rank and whole steps");
         // 1. write this rank's contributions into the owners' staging slots
         PushParams pp;
         memset(&pp, 0, sizeof(pp));
