@@ -129,19 +129,6 @@ class AdamGroup:
         buf = (C.c_ubyte * capi.IPC_HANDLE_BYTES).from_buffer_copy(handle_bytes)
         check(lib().b200opt_ipc_attach(self._h, peer_rank, buf), self._h)
 
-    def attach_process_group(self, all_gather_bytes):
-        """Wires peers living in other processes.
-
-        ``all_gather_bytes(b: bytes) -> list[bytes]`` must return every rank's
-        bytes in rank order (e.g. built on torch.distributed.all_gather_object).
-        """
-        if self.nranks == 1:
-            return
-        handles = all_gather_bytes(self.ipc_export())
-        for q, hb in enumerate(handles):
-            if q != self.rank:
-                self.ipc_attach(q, hb)
-
     def nccl_init(self, unique_id):
         buf = (C.c_ubyte * capi.NCCL_ID_BYTES).from_buffer_copy(unique_id)
         check(lib().b200opt_nccl_init(self._h, buf), self._h)
