@@ -2,6 +2,7 @@
 
   oracle/_ref/saga_e2e_ref    the reference library, unmodified (NCCL build),
                               + its own test/test_classifier.cpp + e2e_main.cpp
+  oracle/_ref/saga_cifar18_*  the same two library builds + e2e_cifar_resnet18.cpp
   oracle/_ref/saga_e2e_b200   the same with the optimizer ops replaced by the
                               b200opt op: the library sources are copied to a
                               scratch directory outside this repository and
@@ -99,6 +100,8 @@ def build_variant(ref, work, name, defines, extra_inc, extra_libs):
     run(NVCC + ["-I" + os.path.join(ref, "src", "cuda"), "-c", os.path.join(ref, KERNELS), "-o", kobj])
     mobj = os.path.join(work, name + "_main.o")
     run(CXX + defines + inc + ["-c", os.path.join(HERE, "e2e_main.cpp"), "-o", mobj])
+    cobj = os.path.join(work, name + "_cifar.o")
+    run(CXX + defines + inc + ["-c", os.path.join(HERE, "e2e_cifar_resnet18.cpp"), "-o", cobj])
     for p in procs:
         out, _ = p.communicate()
         if p.returncode != 0:
@@ -108,7 +111,10 @@ def build_variant(ref, work, name, defines, extra_inc, extra_libs):
     lib_objs, harness_obj = objs[:-1], objs[-1]
     exe = os.path.join(OUT, name)
     run(["g++", "-o", exe] + lib_objs + [kobj, mobj, harness_obj] + LIBS + extra_libs)
-    return exe
+    # the CIFAR-variant ResNet-18 program uses the public API only
+    exe2 = os.path.join(OUT, name.replace("saga_e2e", "saga_cifar18"))
+    run(["g++", "-o", exe2] + lib_objs + [kobj, cobj] + LIBS + extra_libs)
+    return exe + " " + exe2
 
 
 def main():
