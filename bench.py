@@ -3,6 +3,7 @@
 weight all-gather step (the data-parallel parameter update of Saga) on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --gpus N --sweep          (under torch.distributed.run)
 
 N > 1 is launched as one process per GPU by torch.distributed.run; rank 0
 prints ONE JSON line.  A "step" is one optimizer step over the whole flat
@@ -14,10 +15,28 @@ in 64..4 M, renormalised, each padded to 16 elements), fp32 master N(0, 0.02),
 gradients N(0, 1e-3) x loss scale 1024, lr 1e-3, lambda 0.01.  Synthetic,
 seeded; per-step state touched (717 MB at N=1) is larger than L2, so no flush
 is needed between steps.
+
+Legs of the default run (all on the same buffers):
+  value / roofline   K steps back to back on one stream, one CUDA event between
+                     every two steps (mean = ms_per_step, median, min)
+  parity             a small buffer stepped through the SAME collective path at
+                     this N and compared with the CPU oracle (outside all timed
+                     regions; a mismatch makes the run exit non-zero)
+  phases             where the step kernel's time goes (entry wait, body,
+                     completion protocol), from its own %globaltimer stamps
+  nccl_sequence      N > 1: the reference's call sequence on the same buffers
+  peer_copy          N > 1: NVLink bandwidth per direction measured in this run
+  config2_as_written N = 1: gradients regenerated every step from the live loss
+                     scale under the reference policy, +inf every 50th step, L2
+                     flushed before every step
+  e2e                gradients in pinned host memory, copied in every step
+  cpu_baseline       N = 1: the CPU restatement on all host cores
 """
 import argparse
+import importlib.util
 import json
 import os
+import signal
 import sys
 import threading
 import time
@@ -28,14 +47,13 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 TOTAL_PARAMS = 25_600_000
+TENSORS = 160
 LR, L2, SCALE0 = 1e-3, 0.01, 1024.0
-NVLINK_MEASURED_GBS = 770.0   # peer copy per direction measured on this pool
 NVLINK_NOMINAL_GBS = 900.0
 HBM_FALLBACK_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the default one-rank
-# kernel on this workload, from the ncu capture summarised in
-# profiles/staged_step_kernel_n1_config2.md
-NCU_TRAFFIC_N1_BYTES = 660_591_104
+METRIC = ("fused grad-reduce+Adam params/sec (gradient elements reduced and applied per second, "
+          "summed over ranks: N ranks x n parameters / step time)")
+WORKLOAD = "config2: 25.6M fp16 params in 160 tensors, 1 optimizer step"
 
 
 def measured_peaks():
@@ -46,11 +64,31 @@ def measured_peaks():
     return HBM_FALLBACK_GBS, "fallback"
 
 
-def workload():
-    from tests import synth
-    from saga_b200 import FlatLayout
-    sizes = synth.tensor_sizes(TOTAL_PARAMS, 160)
-    return sizes, FlatLayout(sizes)
+def workload_module():
+    """saga_b200/workload.py loaded by file path: numpy-only generators, usable by the
+    reference arm without importing (or mapping the library of) the package."""
+    spec = importlib.util.spec_from_file_location(
+        "b200_workload", os.path.join(ROOT, "saga_b200", "workload.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def padded_layout(sizes):
+    """The reference's flat layout (each tensor padded to 16 elements) in plain Python."""
+    offs, at = [], 0
+    for s in sizes:
+        offs.append(at)
+        at += (int(s) + 15) // 16 * 16
+    return offs, at
+
+
+def base_config(n, tensors, wl=WORKLOAD):
+    """The part of `config` both arms print identically."""
+    return {"workload": wl, "n_params": n, "tensors": tensors, "lr": LR, "l2_lambda": L2,
+            "loss_scale": SCALE0,
+            "l2": "inputs larger than L2: a step streams 4n + 24n/N bytes per GPU (717 MB at "
+                  "N=1, 179 MB at N=8) against 126 MB of L2; no flush between steps"}
 
 
 # ------------------------------------------------------------------ clocks
@@ -110,19 +148,19 @@ class ClockSampler:
         }
 
 
-# ----------------------------------------------------------- CPU baseline leg
+# ----------------------------------------------------------- CPU baseline legs
 
 def cpu_baseline(n, budget_s=12.0, max_steps=5000):
     """The CPU restatement of the reference's adam_kernel_mp (the reference has
     no CPU implementation of this path), all host threads, on the full buffer."""
     from oracle import oracle as orc
-    from tests import synth
+    wl = workload_module()
     orc.use_all_host_threads()
-    w = synth.weights_half(n, seed=1)
+    w = wl.weights_half(n, seed=1)
     c = orc.master_init(w)
     m = np.zeros(n, np.float32)
     v = np.zeros(n, np.float32)
-    g = synth.grads_half(n, SCALE0, 1, seed=1)
+    g = wl.grads_half(n, SCALE0, 1, seed=1)
     b1t, b2t = orc.bias_corrections(1)
     al = orc.alpha(SCALE0)
     for _ in range(2):
@@ -146,48 +184,55 @@ def run_reference_arm(args):
     """--impl reference: the reference has no CPU (or buildable dnnl) training
     path, so this arm times the CPU restatement of its path on all host cores:
     per step the rank-ordered sum of the N ranks' gradient buffers (N > 1) and
-    the mixed-precision Adam update of the same 25.6 M-parameter buffer."""
+    the mixed-precision Adam update of the same 25.6 M-parameter buffer.  It
+    imports nothing of the product: the oracle and the numpy workload only."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from oracle import oracle as orc
-    from tests import synth
+    wl = workload_module()
     cores = orc.use_all_host_threads()
     world = max(args.gpus, 1)
-    sizes, lay = workload()
-    n = lay.total
-    w = synth.weights_half(n, seed=1)
+    sizes = wl.tensor_sizes(TOTAL_PARAMS, TENSORS)
+    _, n = padded_layout(sizes)
+    w = wl.weights_half(n, seed=1)
     c = orc.master_init(w)
     m = np.zeros(n, np.float32)
     v = np.zeros(n, np.float32)
-    grads = [synth.grads_half(n, SCALE0, 1, rank=r, seed=1) for r in range(world)]
+    grads = [wl.grads_half(n, SCALE0, 1, rank=r, seed=1) for r in range(world)]
     gsum = np.empty(n, np.uint16)
     al = orc.alpha(SCALE0)
     steps = min(args.steps, 200)
+    it = [0]
 
-    def one_step(it):
-        b1t, b2t = orc.bias_corrections(it)
+    def one_step():
+        it[0] += 1
+        b1t, b2t = orc.bias_corrections(it[0])
         g = orc.reduce_half_threads(grads, gsum) if world > 1 else grads[0]
         orc.adam_mixed(w, g, m, v, c, al, b1t, b2t, LR, L2, threads=True)
 
-    for it in range(1, args.warmup + 1):
-        one_step(it)
+    # warm by time as well as by count: the thread pool, the page tables of 400 MB of
+    # state and the cores' clocks take a second or two to settle
+    t_warm = time.perf_counter()
+    k = 0
+    while k < args.warmup or time.perf_counter() - t_warm < 2.5:
+        one_step()
+        k += 1
     t0 = time.perf_counter()
-    for it in range(args.warmup + 1, args.warmup + steps + 1):
-        one_step(it)
+    for _ in range(steps):
+        one_step()
     dt = time.perf_counter() - t0
     value = world * n * steps / dt
     sample = (f"{steps} full steps over all {n} parameters"
               + (f", each summing {world} gradient buffers first" if world > 1 else "")
-              + f" ({dt:.1f} s; CPU restatement of src/cuda adam_kernel_mp, OpenMP over elements; "
-                "the reference ships no CPU training path)")
+              + f" ({dt:.1f} s after {k} warm-up steps; CPU restatement of src/cuda adam_kernel_mp, "
+                "OpenMP over elements; the reference ships no CPU training path)")
     line = {
-        "impl": "reference", "metric": "fused grad-reduce+Adam params/sec", "value": value,
-        "unit": "params/s", "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
+        "impl": "reference", "metric": METRIC, "value": value,
+        "unit": "params/s", "n_gpus": args.gpus, "steps": steps, "warmup": k,
         "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config2: 25.6M fp16 params in 160 tensors, 1 optimizer step",
-                   "n_params": n, "tensors": len(sizes)},
+        "config": base_config(n, len(sizes)),
         "cpu_baseline": {"value": value, "unit": "params/s", "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "params/s", "h2d_bytes_per_step": 0,
@@ -205,10 +250,9 @@ def run_serial_ranks(args):
     SM-side cost of one rank's launch, not an NVLink figure, and is not a
     benchmark value."""
     import torch
-    from saga_b200 import AdamGroup, capi
+    from saga_b200 import AdamGroup, FlatLayout, capi, workload
     N = args.serial_ranks
-    sizes, lay = workload()
-    n = args.params or lay.total
+    n = args.params or FlatLayout(workload.tensor_sizes(TOTAL_PARAMS, TENSORS)).total
     dev = torch.device("cuda", 0)
     groups = AdamGroup.create_group([0] * N, n, 0)
     stream = torch.cuda.current_stream(dev)
@@ -251,6 +295,379 @@ def run_serial_ranks(args):
         g.destroy()
 
 
+# ----------------------------------------------------------------- helpers
+
+class Env:
+    """Process-group facts and the helpers every leg needs."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != args.gpus:
+            if self.world == 1 and args.gpus > 1:
+                raise SystemExit("launch N>1 through torch.distributed.run (one process per GPU)")
+            args.gpus = self.world
+        self.dev = torch.device("cuda", self.local)
+        torch.cuda.set_device(self.dev)
+        if self.world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("cpu:gloo,cuda:nccl", rank=self.rank, world_size=self.world,
+                                    device_id=self.dev)
+        self.stream = torch.cuda.current_stream(self.dev)
+        self.sp = self.stream.cuda_stream
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier(device_ids=[self.local])
+        self.torch.cuda.synchronize(self.dev)
+
+    def max_over_ranks(self, values):
+        if self.world == 1:
+            return [float(x) for x in values]
+        t = self.torch.tensor([float(x) for x in values], dtype=self.torch.float64, device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(x) for x in t]
+
+    def all_true(self, flag):
+        if self.world == 1:
+            return bool(flag)
+        t = self.torch.tensor([1 if flag else 0], dtype=self.torch.int32, device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MIN)
+        return bool(int(t[0]))
+
+
+def make_group(env, n_half, n_float, want_path):
+    """One rank's optimizer wired to its peers; returns (group, path actually used).
+    `want_path`: auto | peer | nvls | nccl.  "auto" is the benchmark's own choice: the
+    multicast path where the GPUs offer it and it moves fewer bytes per NVLink
+    direction than the peer path (four ranks and up), the peer path otherwise."""
+    from saga_b200 import AdamGroup, capi, launch
+    flags = 0
+    if env.world > 1 and want_path in ("auto", "nvls"):
+        flags = capi.CREATE_MULTICAST
+    grp = AdamGroup.create(env.rank, env.world, env.local, n_half, n_float, flags)
+    info = {"multicast": False}
+    if env.world > 1:
+        info = launch.wire_process_group(grp, with_nccl=True)
+    path = want_path
+    if want_path == "auto":
+        path = "nvls" if (info["multicast"] and env.world >= 4) else "peer"
+    elif want_path == "nvls" and not info["multicast"]:
+        path = "peer"
+    if env.world == 1:
+        path = "peer"
+    set_path(grp, path)
+    return grp, path, info
+
+
+def set_path(grp, path):
+    from saga_b200 import capi
+    if grp.nranks > 1:
+        grp.set_option(capi.OPT_PATH, {"peer": capi.PATH_PEER, "nvls": capi.PATH_NVLS,
+                                       "nccl": capi.PATH_NCCL}[path])
+
+
+def timed_steps(env, fn, k):
+    """k calls of fn back to back on the stream with one event between every two;
+    returns the per-step device times in ms (this rank)."""
+    torch = env.torch
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(k + 1)]
+    ev[0].record(env.stream)
+    for i in range(k):
+        fn()
+        ev[i + 1].record(env.stream)
+    torch.cuda.synchronize(env.dev)
+    return [ev[i].elapsed_time(ev[i + 1]) for i in range(k)], ev[0].elapsed_time(ev[k])
+
+
+def summarize(per_step_ms):
+    a = np.asarray(per_step_ms, dtype=np.float64) * 1e3
+    return {"mean": float(a.mean()), "median": float(np.median(a)), "min": float(a.min()),
+            "p95": float(np.percentile(a, 95)), "steps": int(a.size)}
+
+
+# ------------------------------------------------------------------ parity leg
+
+def parity_leg(env, path):
+    """A small buffer stepped through the real collective path of this run at this N
+    and compared with the CPU oracle (rank-ordered fp32 sum, the reference's update):
+    2048*6*N+80 fp16 + 528 fp32 parameters, 4 steps, an inf from rank 0 on step 2, a
+    32768 in two shards on step 3.  Returns the block for the JSON line."""
+    import torch
+    from oracle import oracle as orc
+    from saga_b200 import LossScaler, capi, workload
+    N, rank = env.world, env.rank
+    n_half, n_float, steps = 2048 * 6 * N + 80, 528, 4
+    grp, used, _ = make_group(env, n_half, n_float, path)
+    out = {"n_ranks": N, "path": used, "n_half": n_half, "n_float": n_float, "steps": steps}
+    try:
+        W0, Wf0 = workload.weights_half(n_half, seed=17), workload.weights_float(n_float, seed=17)
+        w, g = grp.buffers(capi.HALF)
+        wf, gf = grp.buffers(capi.FLOAT)
+        w.view(torch.int16).copy_(torch.from_numpy(W0.view(np.int16).copy()))
+        wf.copy_(torch.from_numpy(Wf0.copy()))
+        grp.init_master(env.sp)
+        env.barrier()
+        ost = orc.MultiRankState(N, [W0] * N, [Wf0] * N)
+        scaler, oscale = LossScaler(64.0), np.float32(64.0)
+        sh = n_half // N
+        flags_equal = scale_equal = True
+        flag_log = []
+        for step in range(1, steps + 1):
+            G = [workload.grads_half(n_half, oscale, step, rank=r, seed=17) for r in range(N)]
+            Gf = [workload.grads_float(n_float, oscale, step, rank=r, seed=17) for r in range(N)]
+            if step == 2:
+                G[0][n_half // 2 + 3] = 0x7C00
+            if step == 3:
+                G[N - 1][5] = 0x7800
+                G[0][(N - 1) * sh + 9] = 0x7800
+            g.view(torch.int16).copy_(torch.from_numpy(G[rank].view(np.int16).copy()))
+            gf.copy_(torch.from_numpy(Gf[rank].copy()))
+            env.barrier()
+            grp.exec(1e-2, 0.01, scaler.scale, env.sp)
+            flags = grp.flags(env.sp)
+            oflags = ost.step([x.copy() for x in G], [x.copy() for x in Gf], oscale, 1e-2, 0.01)
+            flag_log.append(list(flags))
+            flags_equal &= tuple(flags) == tuple(oflags)
+            scaler.update(flags)
+            oscale = orc.policy_reference(oscale, oflags)
+            scale_equal &= scaler.scale.tobytes() == oscale.tobytes()
+        env.barrier()
+
+        def rel(a, b):      # |a-b| / (|b| + rms(b)): m and the master pass through zero
+            a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+            if not a.size:
+                return 0.0
+            return float(np.max(np.abs(a - b) / (np.abs(b) + np.sqrt(np.mean(b * b)) + 1e-300)))
+        worst = 0.0
+        state_bit_diffs = 0
+        for which, ref in ((0, ost.m[rank]), (1, ost.v[rank]), (2, ost.c[rank])):
+            mine = grp.export_state(capi.HALF, which)
+            worst = max(worst, rel(mine, ref))
+            state_bit_diffs += int(np.count_nonzero(mine.view(np.uint32) != ref.view(np.uint32)))
+        for which, ref in ((0, ost.mf[rank]), (1, ost.vf[rank])):
+            worst = max(worst, rel(grp.export_state(capi.FLOAT, which), ref))
+        mine_w = w.view(torch.int16).cpu().numpy().view(np.uint16)
+        d = np.abs(mine_w.astype(np.int64) - ost.W[0].astype(np.int64))
+        worst, ulp, wdiff, sdiff = env.max_over_ranks(
+            [worst, float(d.max()), float(np.count_nonzero(d)), float(state_bit_diffs)])
+        all_flags = env.all_true(flags_equal)
+        all_scale = env.all_true(scale_equal)
+        out.update({"flags_equal": all_flags, "scale_bits_equal": all_scale,
+                    "max_rel_err": worst, "w_ulp_max": int(ulp), "w_bit_diffs": int(wdiff),
+                    "state_bit_diffs_max_rank": int(sdiff), "flags_per_step": flag_log,
+                    "against": "CPU oracle: rank-ordered fp32 sum, one fp16 rounding, "
+                               "reference update; tolerance 1e-6 per step"})
+        out["ok"] = bool(all_flags and all_scale and worst <= 1e-6 * steps and ulp <= 1)
+    finally:
+        w = g = wf = gf = None
+        env.barrier()
+        grp.destroy()
+    return out
+
+
+# ------------------------------------------------------ config 2 as written
+
+def config2_as_written(env, grp, n, steps):
+    """Config 2 the way it is specified, on one GPU: gradients N(0, 1e-3) x the LIVE loss
+    scale regenerated every step, the reference's policy (x1.02 per clean step, x0.5 on
+    inf/NaN), one +inf injected every 50th step, the flag sums read back and the scale
+    updated on the host every step as Saga's step tail does.  The scale climbs from 1024
+    until gradients overflow by themselves (about 470 steps), then saw-tooths, so steps
+    that take the per-element classification arm (|g| >= 32768) and skipped elements are
+    inside the timed set.  Only the step kernel is between the two events of a step; the
+    gradient generation and an L2 flush (a 256 MB memset) come before the first event."""
+    import torch
+    from saga_b200 import LossScaler, capi
+    dev = env.dev
+    w, g = grp.buffers(capi.HALF)
+    gen = torch.Generator(device=dev).manual_seed(0xC0F2)
+    base = torch.empty(n, dtype=torch.float32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    scaler = LossScaler(SCALE0)
+    times, kinds = [], []
+    evs = []
+    for step in range(1, steps + 1):
+        base.normal_(0.0, 1e-3, generator=gen)
+        torch.mul(base, float(scaler.scale), out=base)
+        g.copy_(base)                       # fp32 -> fp16, overflows to inf by itself
+        if step % 50 == 0:
+            g[int(torch.randint(0, n, (1,), generator=gen, device=dev))] = float("inf")
+        flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(env.stream)
+        grp.exec(LR, L2, scaler.scale, env.sp)
+        b.record(env.stream)
+        flags = grp.flags(env.sp)           # stream sync, as in CudaProgram::step
+        evs.append((a, b))
+        kinds.append("overflow" if (flags[1] or flags[2]) else ("range" if flags[0] else "clean"))
+        scaler.update(flags)
+    times = np.array([a.elapsed_time(b) for a, b in evs]) * 1e3
+    kinds = np.array(kinds)
+    out = {"steps": steps, "us_per_step": summarize(times / 1e3),
+           "final_scale": float(scaler.scale), "l2": "flushed before every step",
+           "policy": "reference (x1.02 clean, x0.9 two range flags, x0.5 inf/NaN)"}
+    for k in ("clean", "range", "overflow"):
+        sel = times[kinds == k]
+        out[k + "_steps"] = int(sel.size)
+        if sel.size:
+            out[k + "_us_median"] = float(np.median(sel))
+    del base, flush
+    return out
+
+
+# ------------------------------------------------------- NVLink copy, this run
+
+def peer_copy_leg(env, mbytes=256):
+    """NVLink bandwidth per direction as this run sees it: a ring of NCCL send/recv
+    (every rank sends `mbytes` MB to the next rank and receives from the previous one, all
+    at once), and one pair alone (rank 0 to rank 1, nothing else on the fabric)."""
+    torch, dist = env.torch, env.dist
+    n = mbytes << 20
+    src = torch.empty(n, dtype=torch.uint8, device=env.dev)
+    dst = torch.empty(n, dtype=torch.uint8, device=env.dev)
+    nxt, prv = (env.rank + 1) % env.world, (env.rank - 1) % env.world
+
+    def ring():
+        ops = [dist.P2POp(dist.isend, src, nxt), dist.P2POp(dist.irecv, dst, prv)]
+        for r in dist.batch_isend_irecv(ops):
+            r.wait()
+
+    def pair():
+        if env.rank == 0:
+            dist.send(src, 1)
+        elif env.rank == 1:
+            dist.recv(dst, 0)
+
+    res = {}
+    for name, fn in (("ring_all_ranks", ring), ("one_pair", pair)):
+        for _ in range(3):
+            fn()
+        env.barrier()
+        k = 10
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(env.stream)
+        for _ in range(k):
+            fn()
+        b.record(env.stream)
+        torch.cuda.synchronize(env.dev)
+        ms = env.max_over_ranks([a.elapsed_time(b) / k])[0]
+        env.barrier()
+        res[name + "_gbs"] = n / (ms * 1e-3) / 1e9
+    res["what"] = f"NCCL send/recv of {mbytes} MB per rank, GB/s per direction per GPU, max over ranks"
+    del src, dst
+    return res
+
+
+# -------------------------------------------------------------- NCCL baselines
+
+def nccl_sequence_leg(env, grp, restore_path, k):
+    """The reference's own sequence (ncclReduceScatter, Adam on the shard, ncclAllGather,
+    3-word all-reduce) on the same buffers."""
+    set_path(grp, "nccl")
+    for _ in range(5):
+        grp.exec(LR, L2, SCALE0, env.sp)
+    grp.flags(env.sp)
+    env.barrier()
+    _, total = timed_steps(env, lambda: grp.exec(LR, L2, SCALE0, env.sp), k)
+    grp.flags(env.sp)
+    env.barrier()
+    set_path(grp, restore_path)
+    return env.max_over_ranks([total / k])[0]
+
+
+def allreduce_sequence_leg(env, n, w, g, k):
+    """The other classic arrangement: all-reduce the whole fp16 gradient buffer (NCCL),
+    then every rank updates ALL parameters with the one-GPU kernel (unsharded state)."""
+    torch, dist = env.torch, env.dist
+    from saga_b200 import bias_corrections
+    from saga_b200 import optimizer as opt_mod
+    aw, ag = w.clone(), g.clone()
+    am, av = torch.zeros(n, device=env.dev), torch.zeros(n, device=env.dev)
+    ac = aw.float()
+    aux = torch.zeros(4, dtype=torch.int32, device=env.dev)
+    b1t, b2t = bias_corrections(1)
+
+    def ar_step():
+        dist.all_reduce(ag, op=dist.ReduceOp.AVG)   # AVG keeps the values bounded over many steps
+        opt_mod.adam_mixed(n, 1.0 / SCALE0, aw.data_ptr(), ag.data_ptr(), am.data_ptr(),
+                           av.data_ptr(), ac.data_ptr(), float(b1t), float(b2t), LR, L2,
+                           aux.data_ptr(), env.sp)
+    for _ in range(3):
+        ar_step()
+    env.barrier()
+    _, total = timed_steps(env, ar_step, k)
+    env.barrier()
+    del aw, ag, am, av, ac
+    return env.max_over_ranks([total / k])[0]
+
+
+# ---------------------------------------------------------------- sweep mode
+
+def run_sweep(args):
+    """BASELINE config 5: flat fp16 buffers of 2^20 .. 2^30 elements at this N; the fused
+    kernel (peer path, and the multicast path where available) against NCCL
+    reduce-scatter + Adam on the shard + all-gather (what the reference does) and NCCL
+    all-reduce + Adam over the whole buffer on every rank.  One JSON line."""
+    env = Env(args)
+    torch = env.torch
+    from saga_b200 import capi
+    rows = []
+    exps = [int(x) for x in args.sweep_exps.split(",")]
+    for e in exps:
+        n = 1 << e
+        k = max(5, min(args.steps, 100 if e <= 26 else (30 if e <= 28 else 10)))
+        grp, _, info = make_group(env, n, 0, "nvls" if env.world > 1 else "peer")
+        w, g = grp.buffers(capi.HALF)
+        gen = torch.Generator(device=env.dev).manual_seed(0x5A6A)
+        chunk = 1 << 26
+        for c0 in range(0, n, chunk):
+            c1 = min(n, c0 + chunk)
+            w[c0:c1] = (torch.randn(c1 - c0, device=env.dev, generator=gen) * 0.02).half()
+        gen_g = torch.Generator(device=env.dev).manual_seed(0x5A6A + 1 + env.rank)
+        for c0 in range(0, n, chunk):
+            c1 = min(n, c0 + chunk)
+            g[c0:c1] = (torch.randn(c1 - c0, device=env.dev, generator=gen_g) * (1e-3 * SCALE0)).half()
+        grp.init_master(env.sp)
+        env.barrier()
+        row = {"log2_n": e, "n": n, "steps": k}
+        paths = ["peer"] + (["nvls"] if info["multicast"] else [])
+        for path in paths:
+            set_path(grp, path)
+            for _ in range(max(3, args.warmup // 4)):
+                grp.exec(LR, L2, SCALE0, env.sp)
+            grp.flags(env.sp)
+            env.barrier()
+            per, total = timed_steps(env, lambda: grp.exec(LR, L2, SCALE0, env.sp), k)
+            grp.flags(env.sp)
+            env.barrier()
+            us = env.max_over_ranks([total / k])[0] * 1e3
+            row["fused_" + path + "_us"] = us
+            if env.world > 1:
+                row["fused_" + path + "_nvlink_gbs_algorithmic"] = \
+                    4 * n * (env.world - 1) / env.world / (us * 1e-6) / 1e9
+            else:
+                row["hbm_gbs"] = 28 * n / (us * 1e-6) / 1e9
+        if env.world > 1:
+            row["nccl_rs_adam_ag_us"] = nccl_sequence_leg(env, grp, "peer", k) * 1e3
+            row["nccl_allreduce_full_adam_us"] = allreduce_sequence_leg(env, n, w, g, k) * 1e3
+        w = g = None
+        env.barrier()
+        grp.destroy()
+        torch.cuda.empty_cache()
+        rows.append(row)
+    if env.rank == 0:
+        print(json.dumps({"mode": "sweep (config 5)", "n_gpus": env.world,
+                          "unit": "us per step, device time, max over ranks", "rows": rows}),
+              flush=True)
+    if env.world > 1:
+        env.dist.destroy_process_group()
+
+
 # ------------------------------------------------------------------- our arm
 
 def main():
@@ -265,7 +682,10 @@ def main():
                     help="put the parameters in the fp32 group (the reference's AdamF32 path: "
                          "fp32 weights and gradients, no master copy) instead of the fp16 group")
     ap.add_argument("--e2e-steps", type=int, default=0, help="default: min(steps, 50)")
+    ap.add_argument("--config2-steps", type=int, default=800,
+                    help="steps of the config-2-as-written leg (N = 1; 0 switches it off)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--with-ref-gpu", action="store_true",
                     help="also time the reference's own compiled Adam kernel (oracle/_ref) as a "
                          "GPU baseline beside the CPU one; off by default")
@@ -273,55 +693,64 @@ def main():
     ap.add_argument("--variant", type=int, default=-1)
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--grid", type=int, default=0)
-    ap.add_argument("--path", default="auto", choices=["auto", "peer", "push", "nccl"])
+    ap.add_argument("--path", default="auto", choices=["auto", "peer", "nvls", "nccl"])
     ap.add_argument("--with-allreduce-baseline", action="store_true",
                     help="N > 1: also time NCCL all-reduce of the whole fp16 gradient buffer followed "
                          "by the one-GPU Adam kernel over all parameters on every rank")
     ap.add_argument("--serial-ranks", type=int, default=0,
                     help="profiling aid: N ranks on ONE GPU, stepped one after the other "
                          "(no cross-GPU waits); times the N-rank kernel against local HBM only")
+    ap.add_argument("--sweep", action="store_true", help="config 5: sizes 2^20..2^30 at this N")
+    ap.add_argument("--sweep-exps", default="20,22,24,26,28,30")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
     if args.serial_ranks:
         return run_serial_ranks(args)
+    if args.sweep:
+        return run_sweep(args)
     args.warmup = max(args.warmup, 3)
 
-    import torch
-    import torch.distributed as dist
-    from saga_b200 import AdamGroup, LossScaler, capi
+    env = Env(args)
+    torch, dist = env.torch, env.dist
+    world, rank, dev, sp = env.world, env.rank, env.dev, env.sp
+    from saga_b200 import FlatLayout, LossScaler, capi, workload
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("launch N>1 through torch.distributed.run (one process per GPU)")
-        args.gpus = world
-    dev = torch.device("cuda", local)
-    torch.cuda.set_device(dev)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world,
-                                device_id=dev)
+    # An orderly exit on SIGTERM (the launcher's way of stopping the other ranks when
+    # one fails): a rank must release its multicast binding itself, not be torn down
+    # while its peers may still address it.
+    live = []
+
+    def on_term(signum, frame):
+        for gx in live:
+            try:
+                torch.cuda.synchronize(dev)
+                gx.destroy()
+            except Exception:
+                pass
+        os._exit(143)
+    signal.signal(signal.SIGTERM, on_term)
 
     if args.params:
         sizes, n = [args.params], (args.params + 15) // 16 * 16
         wl = f"flat fp16 buffer of {n} elements, 1 optimizer step"
     else:
-        sizes, lay = workload()
-        n = lay.total
-        wl = "config2: 25.6M fp16 params in 160 tensors, 1 optimizer step"
+        sizes = workload.tensor_sizes(TOTAL_PARAMS, TENSORS)
+        n = FlatLayout(sizes).total
+        assert n == padded_layout(sizes)[1]
+        wl = WORKLOAD
 
     f32 = args.fp32_group
     if f32:
         wl = wl.replace("fp16", "fp32") + " (fp32 group)"
-    grp = AdamGroup.create(rank, world, local, 0 if f32 else n, n if f32 else 0)
-    if world > 1:
-        from saga_b200 import launch
-        launch.wire_process_group(grp, with_nccl=True)
-        grp.set_option(capi.OPT_PATH, {"auto": capi.PATH_AUTO, "peer": capi.PATH_PEER,
-                                       "push": capi.PATH_PUSH, "nccl": capi.PATH_NCCL}[args.path])
+
+    # ---- parity of this run's collective path at this N, before anything is timed
+    parity = None
+    if not args.no_parity:
+        parity = parity_leg(env, args.path)
+
+    grp, path, info = make_group(env, 0 if f32 else n, n if f32 else 0, args.path)
+    live.append(grp)
     if args.ctas_per_sm:
         grp.set_option(capi.OPT_CTAS_PER_SM, args.ctas_per_sm)
     if args.variant >= 0:
@@ -331,8 +760,6 @@ def main():
     if args.grid:
         grp.set_option(capi.OPT_GRID, args.grid)
 
-    stream = torch.cuda.current_stream(dev)
-    sp = stream.cuda_stream
     w, g = grp.buffers(capi.FLOAT if f32 else capi.HALF)
     gen = torch.Generator(device=dev).manual_seed(0x5A6A)          # same weights on every rank
     w.copy_((torch.randn(n, device=dev, generator=gen) * 0.02).to(w.dtype))
@@ -344,90 +771,65 @@ def main():
     host_ptrs = (0, host_g.data_ptr()) if f32 else (host_g.data_ptr(), 0)
     torch.cuda.synchronize(dev)
 
-    def barrier():
-        if world > 1:
-            dist.barrier(device_ids=[local])
-        torch.cuda.synchronize(dev)
-
-    sampler = ClockSampler(local) if rank == 0 else None
+    sampler = ClockSampler(env.local) if rank == 0 else None
     scaler = LossScaler(SCALE0)
-
-    def timed_steps(k):
-        """k steps back to back on one stream; device time in ms (this rank)."""
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record(stream)
-        for _ in range(k):
-            grp.exec(LR, L2, scaler.scale, sp)
-        b.record(stream)
-        torch.cuda.synchronize(dev)
-        return a.elapsed_time(b)
+    step = lambda: grp.exec(LR, L2, scaler.scale, sp)   # noqa: E731
 
     # ---- device-resident throughput: K steps back to back on one stream
     for _ in range(args.warmup):
-        grp.exec(LR, L2, scaler.scale, sp)
+        step()
     flags = grp.flags(sp)
-    barrier()
+    env.barrier()
     launches0 = grp.launch_count
     if sampler:
         sampler.start()
-    ms = timed_steps(args.steps)
-    barrier()
+    per_step, total_ms = timed_steps(env, step, args.steps)
+    env.barrier()
     launches = grp.launch_count - launches0
     flags = grp.flags(sp)
+    ms = env.max_over_ranks([total_ms])[0]
+    # per-step statistics of the slowest rank's view: element-wise max over ranks
+    per_step = env.max_over_ranks(per_step)
 
-    # ---- N > 1: the reference's own sequence (ncclReduceScatter, Adam on the shard,
-    # ncclAllGather, 3-word all-reduce) on the same buffers, for comparison
+    # ---- where the kernel's time goes: its own timer stamps, read after every step
+    phases = None
+    if world > 1 and path != "nccl":
+        grp.set_option(capi.OPT_PHASE_TIMERS, 1)
+        rows = []
+        for i in range(60):
+            step()
+            grp.flags(sp)
+            if i >= 10:
+                rows.append(grp.phase_times())
+            if world > 1:
+                dist.barrier(device_ids=[env.local])
+        grp.set_option(capi.OPT_PHASE_TIMERS, 0)
+        med = np.median(np.asarray(rows, dtype=np.float64), axis=0) / 1e3
+        med = env.max_over_ranks(list(med))
+        phases = {"entry_wait_us": med[0], "entry_to_last_cta_done_us": med[1],
+                  "completion_protocol_us": med[2], "kernel_total_us": med[3],
+                  "what": "median over 50 steps of the step kernel's own %globaltimer stamps, max "
+                          "over ranks; every step here is followed by a host read of the flags and "
+                          "a host barrier, so the ranks enter each step less tightly aligned than "
+                          "in the back-to-back timed loop"}
+        env.barrier()
+
+    # ---- N > 1: the reference's own sequence on the same buffers, for comparison
     nccl_ms = None
-    if world > 1 and args.path != "nccl":
-        grp.set_option(capi.OPT_PATH, capi.PATH_NCCL)
-        k = min(args.steps, 200)
-        for _ in range(5):
-            grp.exec(LR, L2, scaler.scale, sp)
-        grp.flags(sp)
-        barrier()
-        nccl_ms = timed_steps(k) / k
-        grp.flags(sp)
-        barrier()
-        grp.set_option(capi.OPT_PATH, {"auto": capi.PATH_AUTO, "peer": capi.PATH_PEER,
-                                       "push": capi.PATH_PUSH}[args.path])
+    if world > 1 and path != "nccl":
+        nccl_ms = nccl_sequence_leg(env, grp, path, min(args.steps, 200))
 
-    # ---- N > 1, on request: the other classic arrangement -- all-reduce the whole
-    # gradient buffer (NCCL, fp16), then every rank updates ALL parameters with the
-    # one-GPU kernel (unsharded optimizer state)
     allreduce_ms = None
     if world > 1 and args.with_allreduce_baseline and not f32:
-        from saga_b200 import optimizer as opt_mod
-        from saga_b200 import bias_corrections
-        aw, ag = w.clone(), g.clone()
-        am, av = torch.zeros(n, device=dev), torch.zeros(n, device=dev)
-        ac = aw.float()
-        aux = torch.zeros(4, dtype=torch.int32, device=dev)
-        b1t, b2t = bias_corrections(1)
+        allreduce_ms = allreduce_sequence_leg(env, n, w, g, min(args.steps, 200))
 
-        def ar_step():
-            dist.all_reduce(ag, op=dist.ReduceOp.AVG)   # AVG keeps the values bounded over many steps
-            opt_mod.adam_mixed(n, 1.0 / SCALE0, aw.data_ptr(), ag.data_ptr(), am.data_ptr(),
-                               av.data_ptr(), ac.data_ptr(), float(b1t), float(b2t), LR, L2,
-                               aux.data_ptr(), sp)
-        for _ in range(5):
-            ar_step()
-        barrier()
-        k = min(args.steps, 200)
-        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ea.record(stream)
-        for _ in range(k):
-            ar_step()
-        eb.record(stream)
-        torch.cuda.synchronize(dev)
-        allreduce_ms = ea.elapsed_time(eb) / k
-        barrier()
-        del aw, ag, am, av, ac
+    peer_copy = peer_copy_leg(env) if world > 1 else None
 
     # ---- N = 1, on request: a second baseline beside cpu_baseline -- the reference's own
     # kernel (src/cuda/cuda_kernels.cu compiled unmodified for sm_100a, oracle/_ref) on
     # buffers of the same size
     ref_gpu = None
-    if world == 1 and rank == 0 and args.with_ref_gpu:
+    if world == 1 and rank == 0 and args.with_ref_gpu and not f32:
         from oracle import oracle as orc
         if orc.ref_available():
             R = orc.ref()
@@ -445,13 +847,8 @@ def main():
                 ref_step()
             torch.cuda.synchronize(dev)
             k = min(args.steps, 200)
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record(stream)
-            for _ in range(k):
-                ref_step()
-            b.record(stream)
-            torch.cuda.synchronize(dev)
-            rms = a.elapsed_time(b) / k
+            _, rtotal = timed_steps(env, ref_step, k)
+            rms = rtotal / k
             ref_gpu = {"kernel": "saga::adam_mixed, the reference's src/cuda/cuda_kernels.cu "
                                  "compiled unmodified for sm_100a",
                        "ms_per_step": rms, "value": n / (rms * 1e-3), "unit": "params/s",
@@ -464,22 +861,23 @@ def main():
     e2e_steps = args.e2e_steps or min(args.steps, 50)
     for _ in range(3):
         grp.step_host(host_ptrs[0], host_ptrs[1], LR, L2, scaler.scale, sp)
-    barrier()
+    env.barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         fl = grp.step_host(host_ptrs[0], host_ptrs[1], LR, L2, scaler.scale, sp)
         scaler.update(fl)
     torch.cuda.synchronize(dev)
     e2e_s = time.perf_counter() - t0
-    barrier()
+    env.barrier()
+    e2e_s = env.max_over_ranks([e2e_s])[0]
     clocks = sampler.stop() if sampler else None
 
-    if world > 1:
-        t = torch.tensor([ms, e2e_s, nccl_ms or 0.0, allreduce_ms or 0.0], dtype=torch.float64,
-                         device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_s, nccl_ms = float(t[0]), float(t[1]), float(t[2]) or None
-        allreduce_ms = float(t[3]) or None
+    # ---- N = 1: config 2 as it is written (live scale, injected inf, cold L2)
+    as_written = None
+    if world == 1 and not f32 and not args.params and args.config2_steps > 0:
+        grp.init_master(sp)       # fresh m, v, master for a clean trajectory
+        torch.cuda.synchronize(dev)
+        as_written = config2_as_written(env, grp, n, args.config2_steps)
 
     if rank == 0:
         per_step_ms = ms / args.steps
@@ -491,54 +889,82 @@ def main():
         if f32:  # gradients 4 B read per rank copy, weights 4 B written per rank copy, w/m/v of the shard
             alg_bytes = 8 * n + 20 * n / world
         achieved = alg_bytes / (per_step_ms * 1e-3) / 1e9
+        roof_hbm = {
+            "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+            "frac": achieved / hbm_peak, "traffic": None,
+            "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": alg_bytes,
+            "frac_of_8000_nominal": achieved / 8000.0,
+            "traffic_note": "dram bytes of one launch come from an ncu capture, which this run "
+                            "does not make; the committed summary under profiles/ holds them",
+        }
+        cfg = base_config(n, len(sizes), wl)
+        run = {
+            "value_counts": "gradient elements reduced and applied per second summed over ranks "
+                            "(every rank brings its own n-element gradient buffer: weak scaling)",
+            "unique_params_per_s": n / (per_step_ms * 1e-3),
+            "bytes_streamed_per_gpu_per_step": alg_bytes,
+            "path": path, "path_requested": args.path, "multicast": bool(info["multicast"]),
+        }
         line = {
-            "metric": "fused grad-reduce+Adam params/sec",
+            "metric": METRIC,
             "value": world * n / (per_step_ms * 1e-3),
             "unit": "params/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": per_step_ms,
+            "step_us": summarize(per_step),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {
-                "workload": wl, "n_params": n, "tensors": len(sizes),
-                "value_counts": "gradient parameters reduced and applied per second summed over "
-                                "ranks (every rank brings its own n-element gradient buffer)",
-                "unique_params_per_s": n / (per_step_ms * 1e-3),
-                "l2": "inputs larger than L2: each step streams "
-                      f"{alg_bytes / 1e6:.0f} MB per GPU against 126 MB of L2; no flush",
-                "lr": LR, "l2_lambda": L2, "loss_scale": SCALE0, "path": args.path,
-            },
-            "roofline": {
-                "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                "frac": achieved / hbm_peak,
-                "traffic": NCU_TRAFFIC_N1_BYTES if (world == 1 and not args.params and not f32) else None,
-                "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": alg_bytes,
-                "frac_of_8000_nominal": achieved / 8000.0,
-            },
+            "config": cfg,
+            "run": run,
             "e2e": {
                 "value": world * n * e2e_steps / e2e_s, "unit": "params/s",
                 "h2d_bytes_per_step": (4 if f32 else 2) * n, "d2h_bytes_per_step": 32,
                 "ms_per_step": e2e_s / e2e_steps * 1e3, "steps": e2e_steps,
+                "note": "per step: the gradients travel host to device, the flag sums device to "
+                        "host; the updated weights stay on the device, where the next forward "
+                        "pass reads them (Saga never copies them back during training)",
             },
             "gpu_launches": int(launches),
             "clocks": clocks,
             "flags_last_step": list(flags),
         }
-        if world > 1:
-            nv_bytes = (8 if f32 else 4) * n * (world - 1) / world
-            nv = nv_bytes / (per_step_ms * 1e-3) / 1e9
-            line["roofline_nvlink"] = {
-                "bound": "nvlink", "achieved": nv, "peak": NVLINK_MEASURED_GBS, "unit": "GB/s",
-                "frac": nv / NVLINK_MEASURED_GBS, "frac_of_900_nominal": nv / NVLINK_NOMINAL_GBS,
-                "bytes_per_direction_per_launch": nv_bytes,
-                "note": "with several ranks the step is bound by NVLink, not HBM: this is the "
-                        "binding roofline, `roofline` above is the HBM side of the same launch",
+        if world == 1:
+            line["roofline"] = roof_hbm
+        else:
+            # SURVEY's algorithmic bytes per NVLink direction: reduce-scatter + all-gather of
+            # fp16 (fp32) buffers = 4n(N-1)/N (8n(N-1)/N); what the path in use puts on the
+            # links is reported beside it
+            nv_alg = (8 if f32 else 4) * n * (world - 1) / world
+            nv = nv_alg / (per_step_ms * 1e-3) / 1e9
+            link = (2 * n + 2 * n / world) if (path == "nvls" and not f32) else nv_alg
+            peak = max(peer_copy["one_pair_gbs"], peer_copy["ring_all_ranks_gbs"]) if peer_copy else None
+            line["roofline"] = {
+                "bound": "nvlink", "achieved": nv, "peak": peak or NVLINK_NOMINAL_GBS,
+                "unit": "GB/s per direction per GPU",
+                "frac": nv / (peak or NVLINK_NOMINAL_GBS),
+                "peak_kind": "of measured (NCCL send/recv in this run, the larger of one pair and "
+                             "an all-rank ring)" if peak else "of nominal",
+                "peak_nominal": NVLINK_NOMINAL_GBS, "frac_of_900_nominal": nv / NVLINK_NOMINAL_GBS,
+                "algorithmic_bytes_per_direction_per_launch": nv_alg,
+                "link_bytes_per_direction_of_this_path": link,
+                "link_gbs_of_this_path": link / (per_step_ms * 1e-3) / 1e9,
+                "traffic": None,
+                "note": "achieved = reduce-scatter + all-gather bytes per direction (4n(N-1)/N) / "
+                        "step time; the multicast path moves fewer bytes than that over the links "
+                        "(2n + 2n/N: switch-reduced loads, switch-replicated stores), which is how "
+                        "`frac` can pass the fraction of the link rate a peer-to-peer design reaches",
             }
+            line["roofline_hbm"] = roof_hbm
+            line["peer_copy"] = peer_copy
+            if phases:
+                line["phases"] = phases
             if nccl_ms:
                 line["nccl_sequence"] = {
                     "what": "ncclReduceScatter + Adam kernel on the shard + ncclAllGather + "
                             "3-word ncclAllReduce, the reference's call sequence, same buffers",
                     "ms_per_step": nccl_ms, "speedup_of_fused_kernel": nccl_ms / per_step_ms}
+        if parity is not None:
+            line["parity"] = parity
         if allreduce_ms:
             line["allreduce_sequence"] = {
                 "what": "NCCL all-reduce of the whole fp16 gradient buffer + one-GPU Adam kernel over "
@@ -547,13 +973,20 @@ def main():
         if ref_gpu:
             ref_gpu["speedup_of_fused_kernel"] = ref_gpu["ms_per_step"] / per_step_ms
             line["ref_gpu"] = ref_gpu
+        if as_written:
+            line["config2_as_written"] = as_written
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(n)
         print(json.dumps(line), flush=True)
 
+    w = g = None
+    env.barrier()      # every rank has stopped stepping before any arena is released
+    live.clear()
     grp.destroy()
     if world > 1:
         dist.destroy_process_group()
+    if parity is not None and not parity.get("ok", False):
+        raise SystemExit("parity leg failed: " + json.dumps(parity))
 
 
 if __name__ == "__main__":

@@ -54,21 +54,34 @@ extern "C" {
 #define B200OPT_POLICY_INTERVAL 1  /* halve on inf/nan, double after N clean steps */
 
 /* collective paths for b200opt_set_option(B200OPT_OPT_PATH) */
-#define B200OPT_PATH_AUTO 0 /* peer kernel, NCCL below the measured crossover */
-#define B200OPT_PATH_PEER 1 /* fused peer-memory kernel always */
+#define B200OPT_PATH_AUTO 0 /* peer kernel; NCCL below the measured crossover or when the
+                               GPUs cannot reach one another's memory */
+#define B200OPT_PATH_PEER 1 /* fused peer-memory kernel always: gradients summed in rank
+                               order, bit for bit reproducible */
 #define B200OPT_PATH_NCCL 2 /* ncclReduceScatter + Adam kernel + ncclAllGather */
-#define B200OPT_PATH_PUSH 3 /* ranks store their gradient contributions into the owners' staging
-                               slots, then the fused kernel sums locally: stores only on NVLink */
+#define B200OPT_PATH_NVLS 3 /* fused kernel over an NVSwitch multicast mapping: the switch
+                               sums the gradients (its own order, like NCCL's) and
+                               replicates the weights; needs B200OPT_CREATE_MULTICAST */
 
 /* options */
 #define B200OPT_OPT_TIMEOUT_MS 1    /* limit of every cross-GPU wait (default 10000) */
 #define B200OPT_OPT_PATH 2          /* B200OPT_PATH_* */
 #define B200OPT_OPT_CTAS_PER_SM 3   /* launch shape of the fused kernel (tuning) */
-#define B200OPT_OPT_KERNEL_VARIANT 4 /* 0 = default; 1,6 = direct 16-byte loads; 2..5 = bulk-copy staging through shared memory; 7..10 = the same with one ring per warp */
+#define B200OPT_OPT_KERNEL_VARIANT 4 /* 0 = default of the rank count; 1 = direct 16-byte loads; 2 = bulk-copy staging through shared memory */
 #define B200OPT_OPT_NCCL_CROSSOVER 5 /* AUTO uses NCCL when n_half is below this many elements */
 #define B200OPT_OPT_STAGES 6        /* depth of the shared-memory ring of the staged kernel (tuning) */
-#define B200OPT_OPT_L2_HINT 8       /* staged kernel: 1 loads, 2 stores, 3 both carry an L2 evict-first hint (tuning) */
 #define B200OPT_OPT_GRID 7          /* number of CTAs of the step kernel, overrides CTAS_PER_SM (tuning) */
+#define B200OPT_OPT_PHASE_TIMERS 8  /* 1: the step kernel records where its time went (b200opt_phase_times) */
+#define B200OPT_OPT_ASSUME_NO_PEER_ACCESS 9 /* test aid, set before wiring: treat every other GPU as
+                                               unreachable, as on a machine without peer access */
+
+/* creation flags for b200opt_create_ex / b200opt_create_group_ex */
+#define B200OPT_CREATE_FABRIC 1u    /* weight/gradient arena from CUDA's virtual-memory API: shared
+                                       between processes as a file descriptor (b200opt_fd_export),
+                                       not as a CUDA IPC handle */
+#define B200OPT_CREATE_MULTICAST 2u /* implies FABRIC; b200opt_create_group_ex also binds the arenas
+                                       of all ranks to one NVSwitch multicast object
+                                       (B200OPT_EUNSUPPORTED where the GPUs cannot) */
 
 typedef struct b200opt b200opt_t;
 
@@ -102,6 +115,9 @@ B200OPT_API const char *b200opt_last_error(const b200opt_t *h);
  */
 B200OPT_API int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
                    size_t n_half, size_t n_float);
+/* The same with B200OPT_CREATE_* flags (0 = b200opt_create). */
+B200OPT_API int b200opt_create_ex(b200opt_t **out, int rank, int nranks, int device,
+                      size_t n_half, size_t n_float, unsigned flags);
 
 /*
  * Single-process convenience: creates all ranks and wires them to one another,
@@ -116,8 +132,14 @@ B200OPT_API int b200opt_create(b200opt_t **out, int rank, int nranks, int device
  */
 B200OPT_API int b200opt_create_group(b200opt_t **out, int nranks, const int *devices,
                          size_t n_half, size_t n_float);
+B200OPT_API int b200opt_create_group_ex(b200opt_t **out, int nranks, const int *devices,
+                            size_t n_half, size_t n_float, unsigned flags);
 
-/* Frees everything the handle owns.  Streams belong to the caller. */
+/* Frees everything the handle owns.  Streams belong to the caller.  Ranks that
+ * share a multicast object must all have finished stepping (a host barrier
+ * between the last b200opt_flags and the first b200opt_destroy) before any of
+ * them is destroyed: a rank must never issue a multicast access to memory
+ * another rank has already unbound. */
 B200OPT_API int b200opt_destroy(b200opt_t *h);
 
 /* ------------------------------------------------------------- peer wiring */
@@ -132,8 +154,28 @@ B200OPT_API int b200opt_destroy(b200opt_t *h);
 B200OPT_API int b200opt_ipc_export(b200opt_t *h, void *handle_out);
 B200OPT_API int b200opt_ipc_attach(b200opt_t *h, int peer_rank, const void *handle);
 
-/* Same process, other rank's handle (what b200opt_create_group does). */
+/* Same process, other rank's handle (what b200opt_create_group does).  When
+ * the two GPUs have no peer access the peer is recorded as unreachable instead
+ * of failing: B200OPT_PATH_AUTO then steps through NCCL (b200opt_nccl_init),
+ * the fallback the reference's own path is (src/cuda/cuda_optimizer.cpp:160-185). */
 B200OPT_API int b200opt_attach_local(b200opt_t *h, int peer_rank, b200opt_t *peer);
+
+/*
+ * Wiring of handles created with B200OPT_CREATE_FABRIC, one rank per process:
+ * every rank exports a file descriptor of its arena, the launcher passes it to
+ * every other process (SCM_RIGHTS over a Unix socket) and closes it; every
+ * rank attaches the descriptors it received.  Then, for the multicast path:
+ * rank 0 calls b200opt_mc_create and the launcher passes that descriptor to
+ * the other ranks, which call b200opt_mc_join; after EVERY rank has returned
+ * from create/join (a host barrier) every rank calls b200opt_mc_bind.  No
+ * counterpart in the reference, whose collectives are NCCL's.
+ */
+B200OPT_API int b200opt_fd_export(b200opt_t *h, int *fd);
+B200OPT_API int b200opt_fd_attach(b200opt_t *h, int peer_rank, int fd);
+B200OPT_API int b200opt_multicast_supported(int device, int *yes);
+B200OPT_API int b200opt_mc_create(b200opt_t *h, int *fd);
+B200OPT_API int b200opt_mc_join(b200opt_t *h, int fd);
+B200OPT_API int b200opt_mc_bind(b200opt_t *h);
 
 /*
  * Optional NCCL communicator for the fallback path.  `unique_id` is the 128
@@ -207,7 +249,14 @@ B200OPT_API int b200opt_step(b200opt_t *h, float lr, float l2_lambda, float scal
  * Buckets of one step give bit for bit the result of one b200opt_step.  With
  * several ranks each bucket's kernel waits (bounded) until every rank has
  * issued the same bucket, i.e. until that bucket's gradients are final
- * everywhere.  Not available on the NCCL path.
+ * everywhere.  The kernel then OVERWRITES the bucket's weights in every
+ * rank's weight buffer, without a further barrier for any but the last
+ * bucket.  A bucket may therefore be issued only behind every backward op
+ * that WRITES its gradients AND every backward op that still READS its
+ * weights (a layer's data-gradient op reads the layer's weights), on this
+ * rank's stream; the cross-rank wait then extends that guarantee to all ranks.
+ * A refused bucket moves no counter and leaves the step open.  Not available
+ * on the NCCL path.
  */
 B200OPT_API int b200opt_step_begin(b200opt_t *h);
 B200OPT_API int b200opt_step_bucket(b200opt_t *h, size_t half_first,
@@ -280,6 +329,18 @@ B200OPT_API int b200opt_policy_update(float *scale, const uint32_t flags[3], int
  * computed in double and narrowed to float.  Host-only. */
 B200OPT_API int b200opt_bias_corrections(int iter, float *b1t, float *b2t);
 
+/*
+ * The rule by which a step picks its collective path (B200OPT_PATH_*), from
+ * the requested path and what the group has: several ranks stepped serially
+ * on one GPU, peers' memory reachable, an NCCL communicator, a bound multicast
+ * object.  Returns B200OPT_ESTATE when the requested path lacks its
+ * communicator or multicast object, B200OPT_EUNSUPPORTED when no path is
+ * usable.  Host-only; b200opt_step applies it before it moves any counter.
+ */
+B200OPT_API int b200opt_choose_path(int requested, int nranks, int serial,
+                        int peers_reachable, int have_nccl, int have_multicast,
+                        size_t n_half, size_t nccl_crossover, int *chosen);
+
 /* ------------------------------------------------------------ kernel seam */
 
 /*
@@ -323,8 +384,13 @@ B200OPT_API int b200opt_adam_float(size_t n, float *weights, const float *gradie
  *     (overwritten, not accumulated).
  *   - n may not exceed B200OPT_STATIC_MAX_ELEMS; larger sizes return
  *     B200OPT_ETOOBIG and launch nothing.
- *   - The first call on a device looks up the array's device address; make that
- *     first call during start-up, before any stream capture is open.
+ *   - The first call on a device looks up the array's device address and
+ *     raises the kernel's dynamic shared-memory limit (cudaFuncSetAttribute);
+ *     make that first call during start-up, before any stream capture is open.
+ *   - The kernel's waits on its own asynchronous copies are bounded (10 s).  If
+ *     one ever ran out, the kernel stops early and this entry point reports it
+ *     by writing 0xFFFFFFFF into all three flag words; m, v, master and weights
+ *     are then partly updated.
  *   - All calls on one GPU share the array and it keeps what the last call left:
  *     each call clears the words that must start at zero on `stream` before its
  *     kernel.  Two calls that overlap on the same GPU (different streams, or
@@ -360,6 +426,18 @@ B200OPT_API int b200opt_import_state(b200opt_t *h, int dtype, int which,
 
 B200OPT_API int b200opt_set_option(b200opt_t *h, int option, long value);
 B200OPT_API int b200opt_get_option(const b200opt_t *h, int option, long *value);
+
+/*
+ * With B200OPT_OPT_PHASE_TIMERS set: where the last step kernel of this rank
+ * spent its time, nanoseconds of the GPU's global timer, valid after
+ * b200opt_flags:
+ *   [0] wait for every rank's "gradients final" announcement (first CTA)
+ *   [1] kernel entry until the last CTA finished its share of the shard
+ *   [2] completion protocol in the last CTA (flag exchange, wait until every
+ *       rank has finished reading gradients and writing weights)
+ *   [3] kernel entry until the end of the completion protocol
+ */
+B200OPT_API int b200opt_phase_times(const b200opt_t *h, uint64_t ns_out[4]);
 
 /* Kernel launches this handle has issued since creation (its own kernels and,
  * on the NCCL path, the NCCL calls). */

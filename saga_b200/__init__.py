@@ -6,9 +6,9 @@ The Python layer here is plumbing over that ABI: it mirrors the optimizer ops
 and the step tail of Saga's CUDA backend so that tests and the benchmark can
 drive the library the way Saga's program loop does.
 """
-from . import capi
+from . import capi, workload
 from .optimizer import (AdamGroup, FlatLayout, LossScaler, TrainingStepTail,
                         policy_update, bias_corrections)
 
-__all__ = ["capi", "AdamGroup", "FlatLayout", "LossScaler", "TrainingStepTail",
+__all__ = ["capi", "workload", "AdamGroup", "FlatLayout", "LossScaler", "TrainingStepTail",
            "policy_update", "bias_corrections"]

@@ -12,8 +12,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200opt.so")
 
-SOURCES = ["b200opt.cu", "host_logic.cpp", "nccl_path.cpp"]
-HEADERS = ["fused_step.cuh", "staged_step.cuh", "warp_ring_step.cuh", "push_grads.cuh", "nccl_path.h", os.path.join("..", "..", "include", "b200opt.h")]
+SOURCES = ["b200opt.cu", "host_logic.cpp", "nccl_path.cpp", "fabric.cpp"]
+HEADERS = ["fused_step.cuh", "staged_step.cuh", "nvls_step.cuh", "nccl_path.h", "fabric.h",
+           os.path.join("..", "..", "include", "b200opt.h")]
 
 
 def _nvcc():

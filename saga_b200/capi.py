@@ -13,9 +13,11 @@ OK, EINVAL, ECUDA, ENOMEM, ETIMEOUT, ESTATE, EUNSUPPORTED, ETOOBIG = 0, -1, -2, 
 STATIC_MAX_ELEMS = 1 << 30
 HALF, FLOAT = 0, 1
 POLICY_REFERENCE, POLICY_INTERVAL = 0, 1
-PATH_AUTO, PATH_PEER, PATH_NCCL, PATH_PUSH = 0, 1, 2, 3
+PATH_AUTO, PATH_PEER, PATH_NCCL, PATH_NVLS = 0, 1, 2, 3
 OPT_TIMEOUT_MS, OPT_PATH, OPT_CTAS_PER_SM, OPT_KERNEL_VARIANT, OPT_NCCL_CROSSOVER = 1, 2, 3, 4, 5
-OPT_STAGES, OPT_GRID, OPT_L2_HINT = 6, 7, 8
+OPT_STAGES, OPT_GRID, OPT_PHASE_TIMERS, OPT_ASSUME_NO_PEER_ACCESS = 6, 7, 8, 9
+KERNEL_DIRECT, KERNEL_STAGED = 1, 2
+CREATE_FABRIC, CREATE_MULTICAST = 1, 2
 MAX_RANKS = 8
 IPC_HANDLE_BYTES = 64
 NCCL_ID_BYTES = 128
@@ -30,11 +32,19 @@ SIGNATURES = {
     "b200opt_strerror": (C.c_char_p, [_i]),
     "b200opt_last_error": (C.c_char_p, [_vp]),
     "b200opt_create": (_i, [C.POINTER(_vp), _i, _i, _i, _sz, _sz]),
+    "b200opt_create_ex": (_i, [C.POINTER(_vp), _i, _i, _i, _sz, _sz, C.c_uint]),
     "b200opt_create_group": (_i, [C.POINTER(_vp), _i, C.POINTER(_i), _sz, _sz]),
+    "b200opt_create_group_ex": (_i, [C.POINTER(_vp), _i, C.POINTER(_i), _sz, _sz, C.c_uint]),
     "b200opt_destroy": (_i, [_vp]),
     "b200opt_ipc_export": (_i, [_vp, _vp]),
     "b200opt_ipc_attach": (_i, [_vp, _i, _vp]),
     "b200opt_attach_local": (_i, [_vp, _i, _vp]),
+    "b200opt_fd_export": (_i, [_vp, C.POINTER(_i)]),
+    "b200opt_fd_attach": (_i, [_vp, _i, _i]),
+    "b200opt_multicast_supported": (_i, [_i, C.POINTER(_i)]),
+    "b200opt_mc_create": (_i, [_vp, C.POINTER(_i)]),
+    "b200opt_mc_join": (_i, [_vp, _i]),
+    "b200opt_mc_bind": (_i, [_vp]),
     "b200opt_nccl_unique_id": (_i, [_vp]),
     "b200opt_nccl_init": (_i, [_vp, _vp]),
     "b200opt_buffers": (_i, [_vp, _i, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_sz)]),
@@ -51,6 +61,7 @@ SIGNATURES = {
     "b200opt_device_scale_read": (_i, [_vp, _vp, _fp, _vp, _sz, C.POINTER(_sz)]),
     "b200opt_policy_update": (_i, [_fp, _u32p, _i, C.POINTER(_i), _i]),
     "b200opt_bias_corrections": (_i, [_i, _fp, _fp]),
+    "b200opt_choose_path": (_i, [_i, _i, _i, _i, _i, _i, _sz, _sz, C.POINTER(_i)]),
     "b200opt_adam_mixed": (_i, [_sz, _f, _vp, _vp, _vp, _vp, _vp, _f, _f, _f, _f, _vp, _vp]),
     "b200opt_adam_float": (_i, [_sz, _vp, _vp, _vp, _vp, _f, _f, _f, _f, _vp, _vp]),
     "b200opt_adam_mixed_static": (_i, [_sz, _f, _vp, _vp, _vp, _vp, _vp, _f, _f, _f, _f, _vp, _vp]),
@@ -60,6 +71,7 @@ SIGNATURES = {
     "b200opt_import_state": (_i, [_vp, _i, _i, _vp, _sz]),
     "b200opt_set_option": (_i, [_vp, _i, C.c_long]),
     "b200opt_get_option": (_i, [_vp, _i, C.POINTER(C.c_long)]),
+    "b200opt_phase_times": (_i, [_vp, C.POINTER(C.c_uint64)]),
     "b200opt_launch_count": (_i, [_vp, C.POINTER(C.c_uint64)]),
 }
 
@@ -81,7 +93,7 @@ def lib():
             raise ImportError(
                 f"{LIB_PATH} is missing: build it with `python -m saga_b200.build` "
                 "(nvcc, sm_100a). saga_b200 has no CPU or PyTorch fallback.")
-        handle = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL if False else C.DEFAULT_MODE)
+        handle = C.CDLL(LIB_PATH)
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(handle, name)  # AttributeError if a symbol is missing
             fn.restype = res

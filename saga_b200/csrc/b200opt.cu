@@ -13,10 +13,12 @@
 #include <new>
 #include <string>
 
+#include <unistd.h>
+
+#include "fabric.h"
 #include "fused_step.cuh"
 #include "staged_step.cuh"
-#include "warp_ring_step.cuh"
-#include "push_grads.cuh"
+#include "nvls_step.cuh"
 #include "nccl_path.h"
 
 using namespace b200;
@@ -45,12 +47,19 @@ struct b200opt {
     char *arena = nullptr;
     size_t arena_bytes = 0;
     size_t off_wh = 0, off_gh = 0, off_wf = 0, off_gf = 0;
-    // staging of the push path: nranks slots per dtype group, slot q receives
-    // rank q's contribution to this rank's shard
-    size_t off_sh = 0, off_sf = 0, slot_h_bytes = 0, slot_f_bytes = 0;
     char *peer_arena[kMaxRanks] = {};
     bool peer_is_ipc[kMaxRanks] = {};
+    bool peer_seen[kMaxRanks] = {};
     int peers_attached = 0;
+    // a peer whose memory this GPU cannot reach counts as attached but keeps a
+    // null arena pointer: only the NCCL path can step such a group
+    bool peers_reachable = true;
+    // arena from the virtual-memory API (shareable by fd, bindable to a
+    // multicast object) instead of cudaMalloc
+    bool fabric = false;
+    FabricMapping fab;
+    FabricMapping peer_map[kMaxRanks];
+    FabricMulticast mc;
     // local state
     float *mh = nullptr, *vh = nullptr, *ch = nullptr, *mf = nullptr,
           *vf = nullptr;
@@ -70,7 +79,8 @@ struct b200opt {
     long variant = 0;
     long stages = 0;
     long grid = 0;
-    long l2_hint = 0;
+    long timing = 0;
+    long assume_no_peer_access = 0;  // test aid: wire as if the GPUs had no peer access
     long nccl_crossover = 0;
     uint64_t launches = 0;
     NcclPath *nccl = nullptr;
@@ -170,9 +180,16 @@ void fill_groups(const b200opt *h, StepParams &p, const StepRange &r = StepRange
 }
 
 template <int NR, int UNR, int MINB>
-cudaError_t launch_variant(const StepParams &p, int grid, cudaStream_t st)
+cudaError_t launch_direct(const StepParams &p, int grid, cudaStream_t st)
 {
     fused_step_kernel<NR, UNR, MINB><<<grid, kThreads, 0, st>>>(p);
+    return cudaGetLastError();
+}
+
+template <int NR, int UNR, int MINB>
+cudaError_t launch_nvls(const StepParams &p, int grid, cudaStream_t st)
+{
+    nvls_step_kernel<NR, UNR, MINB><<<grid, kThreads, 0, st>>>(p);
     return cudaGetLastError();
 }
 
@@ -182,27 +199,37 @@ struct LaunchTuning {
     long variant = 0;
     long stages = 0;
     long grid = 0;
-    long l2_hint = 0;
+    bool nvls = false;
 };
 
-template <int NR, int VEC, int THREADS>
-cudaError_t launch_staged(StepParams p, int num_sms, const LaunchTuning &t,
-                          int def_stages, int def_ctas, cudaStream_t st)
+constexpr int kStagedVec = 4, kStagedThreads = 256;
+constexpr int kStagedTile = kStagedVec * kStagedThreads;
+constexpr size_t kSmemBudget = 227 * 1024 - 1024;
+
+// Ring depth of the staged kernel for `cps` CTAs per SM: the rings of all CTAs
+// resident on an SM must fit its shared memory.  0 if not even one stage fits.
+int staged_stages(int nranks, long want, long cps)
 {
-    constexpr int TILE = THREADS * VEC;
-    constexpr size_t per_stage = stage_bytes(NR, TILE);
-    const size_t budget = 227 * 1024 - 1024;
-    const long cps = t.ctas_per_sm > 0 ? t.ctas_per_sm : def_ctas;
-    int stages = (int)(t.stages > 0 ? t.stages : def_stages);
-    // the rings of all CTAs resident on an SM must fit its shared memory
-    while(stages > 1 && (size_t)stages * per_stage * (size_t)cps > budget)
+    const size_t per_stage = stage_bytes(nranks, kStagedTile);
+    int stages = (int)want;
+    while(stages > 1 && (size_t)stages * per_stage * (size_t)cps > kSmemBudget)
         stages--;
     if(stages > kMaxStages)
         stages = kMaxStages;
-    const size_t smem = (size_t)stages * per_stage;
-    if(smem > budget)
+    return (size_t)stages * per_stage <= kSmemBudget ? stages : 0;
+}
+
+template <int NR>
+cudaError_t launch_staged(StepParams p, int num_sms, const LaunchTuning &t,
+                          cudaStream_t st)
+{
+    constexpr int def_stages = 4, def_ctas = 2;
+    const long cps = t.ctas_per_sm > 0 ? t.ctas_per_sm : def_ctas;
+    const int stages = staged_stages(NR, t.stages > 0 ? t.stages : def_stages, cps);
+    if(stages < 1)
         return cudaErrorInvalidValue;
-    auto kern = staged_step_kernel<NR, VEC, THREADS>;
+    const size_t smem = (size_t)stages * stage_bytes(NR, kStagedTile);
+    auto kern = staged_step_kernel<NR, kStagedVec, kStagedThreads>;
     // opting in to large dynamic shared memory is per device and sticky
     static std::atomic<uint64_t> opted{0};
     int dev = 0;
@@ -211,147 +238,99 @@ cudaError_t launch_staged(StepParams p, int num_sms, const LaunchTuning &t,
         return ce;
     if(dev >= 64 || !(opted.load() & (1ull << dev))) {
         ce = cudaFuncSetAttribute(
-            kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
+            kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBudget);
         if(ce != cudaSuccess)
             return ce;
         if(dev < 64)
             opted.fetch_or(1ull << dev);
     }
-    const size_t tiles_h = (p.h.ngroups * kVec + TILE - 1) / TILE;
-    const size_t tiles_f = (p.f.ngroups + THREADS - 1) / THREADS;
+    const size_t tiles_h = (p.h.ngroups * kVec + kStagedTile - 1) / kStagedTile;
+    const size_t tiles_f = (p.f.ngroups + kStagedThreads - 1) / kStagedThreads;
     size_t want = std::max<size_t>(std::max(tiles_h, tiles_f), 1);
     const size_t cap = t.grid > 0 ? (size_t)t.grid : (size_t)num_sms * cps;
     const int grid = (int)std::min<size_t>(want, cap);
     p.stages = stages;
-    p.l2_hint = (int)t.l2_hint;
-    kern<<<grid, THREADS, smem, st>>>(p);
-    return cudaGetLastError();
-}
-
-template <int NR, int VEC, int WARPS>
-cudaError_t launch_warp_ring(StepParams p, int num_sms, const LaunchTuning &t,
-                             int def_stages, int def_ctas, cudaStream_t st)
-{
-    constexpr int TILE = 32 * VEC;
-    constexpr size_t per_stage = stage_bytes(NR, TILE) * WARPS;  // per CTA
-    const size_t budget = 227 * 1024 - 4096;
-    const long cps = t.ctas_per_sm > 0 ? t.ctas_per_sm : def_ctas;
-    int stages = (int)(t.stages > 0 ? t.stages : def_stages);
-    while(stages > 1 && (size_t)stages * per_stage * (size_t)cps > budget)
-        stages--;
-    if(stages > kMaxWarpStages)
-        stages = kMaxWarpStages;
-    const size_t smem = (size_t)stages * per_stage;
-    if(smem > budget)
-        return cudaErrorInvalidValue;
-    auto kern = warp_ring_step_kernel<NR, VEC, WARPS>;
-    static std::atomic<uint64_t> opted{0};
-    int dev = 0;
-    cudaError_t ce = cudaGetDevice(&dev);
-    if(ce != cudaSuccess)
-        return ce;
-    if(dev >= 64 || !(opted.load() & (1ull << dev))) {
-        ce = cudaFuncSetAttribute(
-            kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);
-        if(ce != cudaSuccess)
-            return ce;
-        if(dev < 64)
-            opted.fetch_or(1ull << dev);
-    }
-    const size_t cta_elems = (size_t)TILE * WARPS;
-    const size_t tiles_h = (p.h.ngroups * kVec + cta_elems - 1) / cta_elems;
-    const size_t tiles_f = (p.f.ngroups + WARPS * 32 - 1) / (WARPS * 32);
-    size_t want = std::max<size_t>(std::max(tiles_h, tiles_f), 1);
-    const size_t cap = t.grid > 0 ? (size_t)t.grid : (size_t)num_sms * cps;
-    const int grid = (int)std::min<size_t>(want, cap);
-    p.stages = stages;
-    kern<<<grid, WARPS * 32, smem, st>>>(p);
+    kern<<<grid, kStagedThreads, smem, st>>>(p);
     return cudaGetLastError();
 }
 
 // Launch shape: a persistent grid of ctas_per_sm CTAs on every SM, shrunk for
 // small inputs so that no CTA starts without work.
-//   variant 0: the default of the rank count (4 for one rank)
-//   variant 1: direct loads, one 8-element group per thread per trip
-//   variants 2..5: bulk-copy staging through shared memory
-//     2: 256 threads x 8 elements   3: 128 threads x 8 elements
-//     4: 256 threads x 4 elements   5: 512 threads x 4 elements
-//   variant 6: direct loads, two groups per thread per trip (one rank only)
-//   variants 7..10: bulk-copy staging with one ring per warp (1, 2, 4, 8 ranks)
-//     7: 8 warps x 8 elements/lane    8: 16 warps x 8
-//     9: 16 warps x 4                10: 32 warps x 4
-// Measured on B200s at 25.6 M fp16 parameters.  One rank: variant 4 with two
-// CTAs per SM and four stages 114.9 us; best direct-load shape 119.4 us.
-// Several ranks over NVLink: every shape lands within a few percent of the
-// direct-load kernel (2 ranks 96.7 us, 4 ranks 136.8 us, 8 ranks 163.4 us; the
-// NCCL sequence of the reference takes 229.7 / 319.2 / 394.2 us), so the
-// simplest one, variant 1, is the default there.
+//   variant 0: the default of the rank count (staged for one rank, direct else)
+//   variant 1: direct 16-byte loads, one 8-element group per thread per trip
+//   variant 2: bulk-copy staging through a ring of shared-memory stages
+//              (256 threads x 4 elements per tile)
+// Measured on B200s at 25.6 M fp16 parameters.  One rank: staged, two CTAs per
+// SM, four stages; the direct-load shape is about 4 % slower.  Several ranks
+// over NVLink: both shapes land within a few percent of one another (the
+// links bind, not the SMs), so the simpler direct kernel is the default there.
+// With t.nvls the fp16 group goes through the multicast mapping instead
+// (nvls_step_kernel, direct loads only).
 cudaError_t launch_step(const StepParams &p, int nranks, int num_sms,
                         const LaunchTuning &t, cudaStream_t st)
 {
-    const long variant = t.variant > 0 ? t.variant : (nranks == 1 ? 4 : 1);
-    const long ctas_per_sm = t.ctas_per_sm;
-#define STAGED(NR)                                                         \
-    switch(variant) {                                                      \
-    case 2: return launch_staged<NR, 8, 256>(p, num_sms, t, 4, 2, st);     \
-    case 3: return launch_staged<NR, 8, 128>(p, num_sms, t, 4, 4, st);     \
-    case 4: return launch_staged<NR, 4, 256>(p, num_sms, t, 4, 2, st);     \
-    default: return launch_staged<NR, 4, 512>(p, num_sms, t, 4, 1, st);    \
-    }
-#define WARP_RING(NR)                                                        \
-    switch(variant) {                                                        \
-    case 7: return launch_warp_ring<NR, 8, 8>(p, num_sms, t, 4, 2, st);      \
-    case 8: return launch_warp_ring<NR, 8, 16>(p, num_sms, t, 4, 1, st);     \
-    case 9: return launch_warp_ring<NR, 4, 16>(p, num_sms, t, 4, 2, st);     \
-    default: return launch_warp_ring<NR, 4, 32>(p, num_sms, t, 4, 1, st);    \
-    }
-    if(variant >= 7 && variant <= 10) {
+    const long variant = t.variant > 0 ? t.variant : (nranks == 1 ? 2 : 1);
+    if(variant == 2 && !t.nvls) {
         switch(nranks) {
-        case 1: WARP_RING(1)
-        case 2: WARP_RING(2)
-        case 4: WARP_RING(4)
-        case 8: WARP_RING(8)
+        case 1: return launch_staged<1>(p, num_sms, t, st);
+        case 2: return launch_staged<2>(p, num_sms, t, st);
+        case 3: return launch_staged<3>(p, num_sms, t, st);
+        case 4: return launch_staged<4>(p, num_sms, t, st);
+        case 5: return launch_staged<5>(p, num_sms, t, st);
+        case 6: return launch_staged<6>(p, num_sms, t, st);
+        case 7: return launch_staged<7>(p, num_sms, t, st);
+        case 8: return launch_staged<8>(p, num_sms, t, st);
         }
         return cudaErrorInvalidValue;
     }
-#undef WARP_RING
-    if(variant >= 2 && variant <= 5) {
-        switch(nranks) {
-        case 1: STAGED(1)
-        case 2: STAGED(2)
-        case 3: STAGED(3)
-        case 4: STAGED(4)
-        case 5: STAGED(5)
-        case 6: STAGED(6)
-        case 7: STAGED(7)
-        case 8: STAGED(8)
-        }
-        return cudaErrorInvalidValue;
-    }
-#undef STAGED
     const size_t groups = std::max(p.h.ngroups, p.f.ngroups);
-    const int unr = (nranks == 1 && variant == 6) ? 2 : 1;
     // measured at 25.6 M parameters: 2 CTAs per SM up to four ranks, 3 beyond
-    const long def_ctas = nranks <= 4 ? 2 : 3;
-    const long cps = ctas_per_sm > 0 ? ctas_per_sm : def_ctas;
-    size_t want = (groups + (size_t)kThreads * unr - 1) / ((size_t)kThreads * unr);
+    const long def_ctas = t.nvls ? 3 : (nranks <= 4 ? 2 : 3);
+    const long cps = t.ctas_per_sm > 0 ? t.ctas_per_sm : def_ctas;
+    size_t want = (groups + (size_t)kThreads - 1) / (size_t)kThreads;
     if(want == 0)
         want = 1;
     const int grid = (int)std::min<size_t>(
         want, t.grid > 0 ? (size_t)t.grid : (size_t)num_sms * cps);
+    if(t.nvls) {
+        switch(nranks) {
+        case 2: return launch_nvls<2, 1, 3>(p, grid, st);
+        case 3: return launch_nvls<3, 1, 3>(p, grid, st);
+        case 4: return launch_nvls<4, 1, 3>(p, grid, st);
+        case 5: return launch_nvls<5, 1, 3>(p, grid, st);
+        case 6: return launch_nvls<6, 1, 3>(p, grid, st);
+        case 7: return launch_nvls<7, 1, 3>(p, grid, st);
+        case 8: return launch_nvls<8, 1, 3>(p, grid, st);
+        }
+        return cudaErrorInvalidValue;
+    }
     switch(nranks) {
-    case 1:
-        return variant == 6 ? launch_variant<1, 2, 2>(p, grid, st)
-                            : launch_variant<1, 1, 3>(p, grid, st);
-    case 2: return launch_variant<2, 1, 3>(p, grid, st);
-    case 3: return launch_variant<3, 1, 2>(p, grid, st);
-    case 4: return launch_variant<4, 1, 2>(p, grid, st);
-    case 5: return launch_variant<5, 1, 2>(p, grid, st);
-    case 6: return launch_variant<6, 1, 2>(p, grid, st);
-    case 7: return launch_variant<7, 1, 2>(p, grid, st);
-    case 8: return launch_variant<8, 1, 2>(p, grid, st);
+    case 1: return launch_direct<1, 1, 3>(p, grid, st);
+    case 2: return launch_direct<2, 1, 3>(p, grid, st);
+    case 3: return launch_direct<3, 1, 2>(p, grid, st);
+    case 4: return launch_direct<4, 1, 2>(p, grid, st);
+    case 5: return launch_direct<5, 1, 2>(p, grid, st);
+    case 6: return launch_direct<6, 1, 2>(p, grid, st);
+    case 7: return launch_direct<7, 1, 2>(p, grid, st);
+    case 8: return launch_direct<8, 1, 2>(p, grid, st);
     }
     return cudaErrorInvalidValue;
+}
+
+// Would launch_step refuse this combination?  Checked before a step moves any
+// counter, so that a refused step leaves the rank in step with its peers.
+bool launch_possible(int nranks, const LaunchTuning &t)
+{
+    if(nranks < 1 || nranks > kMaxRanks)
+        return false;
+    if(t.nvls)
+        return nranks >= 2;
+    const long variant = t.variant > 0 ? t.variant : (nranks == 1 ? 2 : 1);
+    if(variant == 2) {
+        const long cps = t.ctas_per_sm > 0 ? t.ctas_per_sm : 2;
+        return staged_stages(nranks, t.stages > 0 ? t.stages : 4, cps) >= 1;
+    }
+    return variant == 1;
 }
 
 LaunchTuning tuning_of(const b200opt *h)
@@ -361,7 +340,6 @@ LaunchTuning tuning_of(const b200opt *h)
     t.variant = h->variant;
     t.stages = h->stages;
     t.grid = h->grid;
-    t.l2_hint = h->l2_hint;
     return t;
 }
 
@@ -400,11 +378,11 @@ const char *b200opt_last_error(const b200opt_t *h)
     return h ? h->err.c_str() : "";
 }
 
-int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
-                   size_t n_half, size_t n_float)
+int b200opt_create_ex(b200opt_t **out, int rank, int nranks, int device,
+                      size_t n_half, size_t n_float, unsigned flags)
 {
     if(!out || nranks < 1 || nranks > kMaxRanks || rank < 0 || rank >= nranks ||
-       device < 0)
+       device < 0 || (flags & ~(B200OPT_CREATE_FABRIC | B200OPT_CREATE_MULTICAST)))
         return B200OPT_EINVAL;
     *out = nullptr;
     int ndev = 0;
@@ -419,6 +397,7 @@ int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
     h->device = device;
     h->n_half = n_half;
     h->n_float = n_float;
+    h->fabric = flags != 0;
     // the reference's partition: plain integer division
     // (src/cuda/cuda_optimizer.cpp:85-86,157-158 of the Saga tree)
     h->sh = n_half / nranks;
@@ -432,17 +411,12 @@ int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
     h->off_gh = h->off_wh + round_up(n_half * 2, 256);
     h->off_wf = h->off_gh + round_up(n_half * 2, 256);
     h->off_gf = h->off_wf + round_up(n_float * 4, 256);
-    h->off_sh = h->off_gf + round_up(n_float * 4, 256);
-    if(nranks > 1) {
-        h->slot_h_bytes = h->sh ? round_up((h->sh + kStateAlign + 2 * kVec) * 2, 256) : 0;
-        h->slot_f_bytes = h->sf ? round_up((h->sf + kStateAlign + 2 * kVec) * 4, 256) : 0;
-    }
-    h->off_sf = h->off_sh + h->slot_h_bytes * nranks;
-    h->arena_bytes = h->off_sf + h->slot_f_bytes * nranks;
+    h->arena_bytes = h->off_gf + round_up(n_float * 4, 256);
 
     DeviceGuard guard(device);
     int rc = B200OPT_OK;
     cudaError_t ce = cudaSuccess;
+    std::string ferr;
     do {
         if(!guard.ok) {
             rc = B200OPT_ECUDA;
@@ -454,7 +428,18 @@ int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
             break;
         }
         h->num_sms = prop.multiProcessorCount;
-        if((ce = cudaMalloc(&h->arena, h->arena_bytes)) != cudaSuccess) {
+        if(h->fabric) {
+            // every rank of the group rounds to the same size, so that the
+            // arenas can be bound to one multicast object at offset 0
+            size_t gran = 0;
+            if((rc = fabric_granularity(device, nranks, true, &gran, &ferr)) != 0 &&
+               (rc = fabric_granularity(device, nranks, false, &gran, &ferr)) != 0)
+                break;
+            h->arena_bytes = round_up(h->arena_bytes, gran);
+            if((rc = fabric_alloc(&h->fab, device, h->arena_bytes, &ferr)) != 0)
+                break;
+            h->arena = reinterpret_cast<char *>(h->fab.va);
+        } else if((ce = cudaMalloc(&h->arena, h->arena_bytes)) != cudaSuccess) {
             rc = B200OPT_ENOMEM;
             break;
         }
@@ -467,11 +452,9 @@ int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
         h->state_f_elems = h->sf ? round_up(h->of + h->sf - h->Af, kVec) : 0;
         // one allocation for all shard state: [m | v | master | m32 | v32]
         {
-            const size_t skew = 0;
             const size_t hb = round_up(h->state_h_elems * 4, 256);
             const size_t fb = round_up(h->state_f_elems * 4, 256);
-            const size_t hstride = hb ? hb + skew : 0;
-            h->state_bytes = 3 * hstride + 2 * fb;
+            h->state_bytes = 3 * hb + 2 * fb;
             if(h->state_bytes) {
                 if((ce = cudaMalloc(&h->state, h->state_bytes)) != cudaSuccess) {
                     rc = B200OPT_ENOMEM;
@@ -483,12 +466,12 @@ int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
                 }
                 if(hb) {
                     h->mh = (float *)(h->state);
-                    h->vh = (float *)(h->state + hstride);
-                    h->ch = (float *)(h->state + 2 * hstride);
+                    h->vh = (float *)(h->state + hb);
+                    h->ch = (float *)(h->state + 2 * hb);
                 }
                 if(fb) {
-                    h->mf = (float *)(h->state + 3 * hstride);
-                    h->vf = (float *)(h->state + 3 * hstride + fb);
+                    h->mf = (float *)(h->state + 3 * hb);
+                    h->vf = (float *)(h->state + 3 * hb + fb);
                 }
             }
         }
@@ -511,6 +494,7 @@ int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
     } while(0);
     if(rc) {
         (void)ce;
+        cudaGetLastError();
         b200opt_destroy(h);
         return rc;
     }
@@ -518,6 +502,12 @@ int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
     h->peers_attached = 1;
     *out = h;
     return B200OPT_OK;
+}
+
+int b200opt_create(b200opt_t **out, int rank, int nranks, int device,
+                   size_t n_half, size_t n_float)
+{
+    return b200opt_create_ex(out, rank, nranks, device, n_half, n_float, 0);
 }
 
 int b200opt_destroy(b200opt_t *h)
@@ -528,15 +518,25 @@ int b200opt_destroy(b200opt_t *h)
     cudaDeviceSynchronize();
     if(h->nccl)
         nccl_path_destroy(h->nccl);
+    // the multicast view goes first: unmap, unbind this GPU's memory, drop the
+    // handle; only then the memory that was bound to it
+    fabric_mc_release(&h->mc);
     for(int q = 0; q < h->nranks; q++) {
-        if(q != h->rank && h->peer_arena[q] && h->peer_is_ipc[q])
+        if(q == h->rank || !h->peer_arena[q])
+            continue;
+        if(h->peer_is_ipc[q])
             cudaIpcCloseMemHandle(h->peer_arena[q]);
+        fabric_unmap(&h->peer_map[q]);
     }
-    cudaFree(h->arena);
+    if(h->fabric)
+        fabric_unmap(&h->fab);
+    else
+        cudaFree(h->arena);
     cudaFree(h->state);
     cudaFree(h->scale_log);
     if(h->host)
         cudaFreeHost(h->host);
+    cudaGetLastError();
     delete h;
     return B200OPT_OK;
 }
@@ -549,42 +549,96 @@ int b200opt_attach_local(b200opt_t *h, int peer_rank, b200opt_t *peer)
         return B200OPT_EINVAL;
     if(peer->n_half != h->n_half || peer->n_float != h->n_float)
         return fail(h, B200OPT_EINVAL, "peer was created with other sizes");
-    if(h->peer_arena[peer_rank])
+    if(peer->fabric != h->fabric)
+        return fail(h, B200OPT_EINVAL, "peer was created with other creation flags");
+    if(h->peer_seen[peer_rank])
         return fail(h, B200OPT_ESTATE, "peer already attached");
+    bool reachable = true;
     if(peer->device == h->device) {
         h->serial = true;
     } else {
         DeviceGuard guard(h->device);
         int can = 0;
         CK(h, cudaDeviceCanAccessPeer(&can, h->device, peer->device));
-        if(!can)
-            return fail(h, B200OPT_EUNSUPPORTED,
-                        "no peer access between the two devices");
-        cudaError_t ce = cudaDeviceEnablePeerAccess(peer->device, 0);
-        if(ce == cudaErrorPeerAccessAlreadyEnabled)
-            cudaGetLastError();
-        else if(ce != cudaSuccess)
-            return fail(h, B200OPT_ECUDA, "cudaDeviceEnablePeerAccess", ce);
+        if(h->assume_no_peer_access)
+            can = 0;
+        if(!can) {
+            // counted as attached without memory: the NCCL path can still step
+            reachable = false;
+        } else if(h->fabric) {
+            std::string err;
+            int rc = fabric_grant(peer->fab, h->device, &err);
+            if(rc)
+                return fail(h, rc, err.c_str());
+        } else {
+            cudaError_t ce = cudaDeviceEnablePeerAccess(peer->device, 0);
+            if(ce == cudaErrorPeerAccessAlreadyEnabled)
+                cudaGetLastError();
+            else if(ce != cudaSuccess)
+                return fail(h, B200OPT_ECUDA, "cudaDeviceEnablePeerAccess", ce);
+        }
     }
-    h->peer_arena[peer_rank] = peer->arena;
+    if(reachable)
+        h->peer_arena[peer_rank] = peer->arena;
+    else
+        h->peers_reachable = false;
+    h->peer_seen[peer_rank] = true;
     h->peers_attached++;
     return B200OPT_OK;
 }
 
-int b200opt_create_group(b200opt_t **out, int nranks, const int *devices,
-                         size_t n_half, size_t n_float)
+static int group_multicast(b200opt_t **hs, int nranks)
+{
+    // rank 0 creates the object; the others take their own reference to it
+    // through a file descriptor, exactly as separate processes would
+    b200opt *h0 = hs[0];
+    std::string err;
+    int rc = fabric_mc_create(&h0->mc, nranks, h0->arena_bytes, &err);
+    if(rc)
+        return fail(h0, rc, err.c_str());
+    int fd = -1;
+    rc = fabric_export_fd(h0->mc.mc, &fd, &err);
+    if(rc)
+        return fail(h0, rc, err.c_str());
+    for(int r = 1; r < nranks && !rc; r++) {
+        DeviceGuard guard(hs[r]->device);
+        rc = fabric_mc_import(&hs[r]->mc, fd, hs[r]->arena_bytes, &err);
+        if(rc)
+            fail(hs[r], rc, err.c_str());
+    }
+    close(fd);
+    for(int r = 0; r < nranks && !rc; r++) {
+        DeviceGuard guard(hs[r]->device);
+        rc = fabric_mc_add_device(&hs[r]->mc, hs[r]->device, &err);
+        if(rc)
+            fail(hs[r], rc, err.c_str());
+    }
+    for(int r = 0; r < nranks && !rc; r++) {
+        DeviceGuard guard(hs[r]->device);
+        rc = fabric_mc_bind(&hs[r]->mc, hs[r]->fab, hs[r]->device, &err);
+        if(rc)
+            fail(hs[r], rc, err.c_str());
+    }
+    return rc;
+}
+
+int b200opt_create_group_ex(b200opt_t **out, int nranks, const int *devices,
+                            size_t n_half, size_t n_float, unsigned flags)
 {
     if(!out || !devices || nranks < 1 || nranks > kMaxRanks)
         return B200OPT_EINVAL;
     for(int r = 0; r < nranks; r++)
         out[r] = nullptr;
-    int rc = B200OPT_OK;
-    for(int r = 0; r < nranks && !rc; r++)
-        rc = b200opt_create(&out[r], r, nranks, devices[r], n_half, n_float);
     bool any_shared = false;
     for(int r = 0; r < nranks; r++)
         for(int q = 0; q < r; q++)
             any_shared |= devices[r] == devices[q];
+    if((flags & B200OPT_CREATE_MULTICAST) && (any_shared || nranks < 2))
+        return B200OPT_EUNSUPPORTED;
+    int rc = B200OPT_OK;
+    for(int r = 0; r < nranks && !rc; r++)
+        rc = b200opt_create_ex(&out[r], r, nranks, devices[r], n_half, n_float,
+                               flags);
     for(int r = 0; r < nranks && !rc; r++)
         for(int q = 0; q < nranks && !rc; q++)
             if(q != r)
@@ -592,6 +646,8 @@ int b200opt_create_group(b200opt_t **out, int nranks, const int *devices,
     if(!rc && any_shared)
         for(int r = 0; r < nranks; r++)
             out[r]->serial = true;
+    if(!rc && (flags & B200OPT_CREATE_MULTICAST))
+        rc = group_multicast(out, nranks);
     if(rc) {
         for(int r = 0; r < nranks; r++) {
             if(out[r])
@@ -602,10 +658,19 @@ int b200opt_create_group(b200opt_t **out, int nranks, const int *devices,
     return rc;
 }
 
+int b200opt_create_group(b200opt_t **out, int nranks, const int *devices,
+                         size_t n_half, size_t n_float)
+{
+    return b200opt_create_group_ex(out, nranks, devices, n_half, n_float, 0);
+}
+
 int b200opt_ipc_export(b200opt_t *h, void *handle_out)
 {
     if(!h || !handle_out)
         return B200OPT_EINVAL;
+    if(h->fabric)
+        return fail(h, B200OPT_EUNSUPPORTED,
+                    "this arena is shared by file descriptor (b200opt_fd_export)");
     static_assert(sizeof(cudaIpcMemHandle_t) == B200OPT_IPC_HANDLE_BYTES,
                   "IPC handle size");
     DeviceGuard guard(h->device);
@@ -620,16 +685,134 @@ int b200opt_ipc_attach(b200opt_t *h, int peer_rank, const void *handle)
     if(!h || !handle || peer_rank < 0 || peer_rank >= h->nranks ||
        peer_rank == h->rank)
         return B200OPT_EINVAL;
-    if(h->peer_arena[peer_rank])
+    if(h->peer_seen[peer_rank])
         return fail(h, B200OPT_ESTATE, "peer already attached");
     DeviceGuard guard(h->device);
     cudaIpcMemHandle_t mh;
     memcpy(&mh, handle, sizeof(mh));
     void *p = nullptr;
-    CK(h, cudaIpcOpenMemHandle(&p, mh, cudaIpcMemLazyEnablePeerAccess));
-    h->peer_arena[peer_rank] = (char *)p;
-    h->peer_is_ipc[peer_rank] = true;
+    cudaError_t ce = h->assume_no_peer_access
+                         ? cudaErrorPeerAccessUnsupported
+                         : cudaIpcOpenMemHandle(&p, mh, cudaIpcMemLazyEnablePeerAccess);
+    if(ce == cudaErrorPeerAccessUnsupported) {
+        // counted as attached without memory: the NCCL path can still step
+        cudaGetLastError();
+        h->peers_reachable = false;
+    } else if(ce != cudaSuccess) {
+        return fail(h, B200OPT_ECUDA, "cudaIpcOpenMemHandle", ce);
+    } else {
+        h->peer_arena[peer_rank] = (char *)p;
+        h->peer_is_ipc[peer_rank] = true;
+    }
+    h->peer_seen[peer_rank] = true;
     h->peers_attached++;
+    return B200OPT_OK;
+}
+
+int b200opt_fd_export(b200opt_t *h, int *fd)
+{
+    if(!h || !fd)
+        return B200OPT_EINVAL;
+    if(!h->fabric)
+        return fail(h, B200OPT_EUNSUPPORTED,
+                    "this arena is shared by CUDA IPC handle (b200opt_ipc_export)");
+    DeviceGuard guard(h->device);
+    std::string err;
+    int rc = fabric_export_fd(h->fab.mem, fd, &err);
+    return rc ? fail(h, rc, err.c_str()) : B200OPT_OK;
+}
+
+int b200opt_fd_attach(b200opt_t *h, int peer_rank, int fd)
+{
+    if(!h || fd < 0 || peer_rank < 0 || peer_rank >= h->nranks ||
+       peer_rank == h->rank)
+        return B200OPT_EINVAL;
+    if(!h->fabric)
+        return fail(h, B200OPT_EUNSUPPORTED, "created without B200OPT_CREATE_FABRIC");
+    if(h->peer_seen[peer_rank])
+        return fail(h, B200OPT_ESTATE, "peer already attached");
+    DeviceGuard guard(h->device);
+    std::string err;
+    int rc = fabric_import(&h->peer_map[peer_rank], fd, h->device, h->arena_bytes,
+                           &err);
+    if(rc)
+        return fail(h, rc, err.c_str());
+    h->peer_arena[peer_rank] = reinterpret_cast<char *>(h->peer_map[peer_rank].va);
+    h->peer_seen[peer_rank] = true;
+    h->peers_attached++;
+    return B200OPT_OK;
+}
+
+int b200opt_multicast_supported(int device, int *yes)
+{
+    if(!yes || device < 0)
+        return B200OPT_EINVAL;
+    DeviceGuard guard(device);
+    bool y = false;
+    std::string err;
+    int rc = fabric_multicast_supported(device, &y, &err);
+    *yes = y ? 1 : 0;
+    return rc;
+}
+
+int b200opt_mc_create(b200opt_t *h, int *fd)
+{
+    if(!h || !fd)
+        return B200OPT_EINVAL;
+    if(!h->fabric || h->nranks < 2 || h->serial)
+        return fail(h, B200OPT_EUNSUPPORTED,
+                    "a multicast object needs B200OPT_CREATE_FABRIC and one GPU per rank");
+    if(h->mc.mc)
+        return fail(h, B200OPT_ESTATE, "multicast object already present");
+    DeviceGuard guard(h->device);
+    std::string err;
+    int rc = fabric_mc_create(&h->mc, h->nranks, h->arena_bytes, &err);
+    if(!rc)
+        rc = fabric_export_fd(h->mc.mc, fd, &err);
+    if(!rc)
+        rc = fabric_mc_add_device(&h->mc, h->device, &err);
+    if(rc) {
+        fabric_mc_release(&h->mc);
+        return fail(h, rc, err.c_str());
+    }
+    return B200OPT_OK;
+}
+
+int b200opt_mc_join(b200opt_t *h, int fd)
+{
+    if(!h || fd < 0)
+        return B200OPT_EINVAL;
+    if(!h->fabric || h->nranks < 2 || h->serial)
+        return fail(h, B200OPT_EUNSUPPORTED,
+                    "a multicast object needs B200OPT_CREATE_FABRIC and one GPU per rank");
+    if(h->mc.mc)
+        return fail(h, B200OPT_ESTATE, "multicast object already present");
+    DeviceGuard guard(h->device);
+    std::string err;
+    int rc = fabric_mc_import(&h->mc, fd, h->arena_bytes, &err);
+    if(!rc)
+        rc = fabric_mc_add_device(&h->mc, h->device, &err);
+    if(rc) {
+        fabric_mc_release(&h->mc);
+        return fail(h, rc, err.c_str());
+    }
+    return B200OPT_OK;
+}
+
+int b200opt_mc_bind(b200opt_t *h)
+{
+    if(!h)
+        return B200OPT_EINVAL;
+    if(!h->mc.mc || h->mc.bound)
+        return fail(h, B200OPT_ESTATE,
+                    "b200opt_mc_create / b200opt_mc_join first, and bind once");
+    DeviceGuard guard(h->device);
+    std::string err;
+    int rc = fabric_mc_bind(&h->mc, h->fab, h->device, &err);
+    if(rc) {
+        fabric_mc_release(&h->mc);
+        return fail(h, rc, err.c_str());
+    }
     return B200OPT_OK;
 }
 
@@ -710,27 +893,38 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
                     "an earlier step timed out; the handle is unusable");
     if(h->peers_attached != h->nranks)
         return fail(h, B200OPT_ESTATE, "not every peer rank is attached");
-    // everything that can refuse the call is checked before any counter moves
-    const bool use_nccl =
-        h->nranks > 1 && !h->serial &&
-        (h->path == B200OPT_PATH_NCCL ||
-         (h->path == B200OPT_PATH_AUTO && h->nccl &&
-          (long)h->n_half < h->nccl_crossover));
+    // Everything that can refuse the call is checked before any counter moves:
+    // a rank whose step was refused must not run one epoch and one Adam
+    // iteration ahead of its peers.
+    int path = B200OPT_PATH_PEER;
+    int rc = b200opt_choose_path((int)h->path, h->nranks, h->serial ? 1 : 0,
+                                 h->peers_reachable ? 1 : 0, h->nccl ? 1 : 0,
+                                 h->mc.va ? 1 : 0, h->n_half,
+                                 (size_t)h->nccl_crossover, &path);
+    if(rc == B200OPT_ESTATE)
+        return fail(h, rc,
+                    (int)h->path == B200OPT_PATH_NVLS
+                        ? "multicast path selected but no multicast object is bound"
+                        : "NCCL path selected but b200opt_nccl_init was not called");
+    if(rc)
+        return fail(h, rc,
+                    "no collective path is usable: this GPU cannot reach a peer's "
+                    "memory and there is no NCCL communicator (or the requested "
+                    "path needs one GPU per rank)");
+    const bool use_nccl = path == B200OPT_PATH_NCCL;
+    LaunchTuning tune = tuning_of(h);
+    tune.nvls = path == B200OPT_PATH_NVLS;
     if(use_nccl) {
         if(!range.whole)
             return fail(h, B200OPT_EUNSUPPORTED,
-                        "bucketed steps need the peer-kernel path");
+                        "bucketed steps need a peer-memory path");
         if(device_scale)
             return fail(h, B200OPT_EUNSUPPORTED,
-                        "the device-resident loss scale needs the peer-kernel path");
-        if(!h->nccl)
-            return fail(h, B200OPT_ESTATE,
-                        "NCCL path selected but b200opt_nccl_init was not called");
-    } else if(h->path == B200OPT_PATH_PUSH && h->nranks > 1 &&
-              (h->serial || !range.whole)) {
-        return fail(h, B200OPT_EUNSUPPORTED,
-                    "the push path needs one GPU per rank and whole steps");
+                        "the device-resident loss scale needs a peer-memory path");
     }
+    if(!launch_possible(use_nccl ? 1 : h->nranks, tune))
+        return fail(h, B200OPT_EINVAL,
+                    "kernel variant / stage options do not fit this rank count");
     DeviceGuard guard(h->device);
     cudaStream_t st = (cudaStream_t)stream;
 
@@ -751,6 +945,7 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
     p.epoch = ++h->epoch;
     p.timeout_ns = (unsigned long long)h->timeout_ms * 1000000ull;
     p.host = h->host_dev;
+    p.timing = h->timing ? 1 : 0;
 
     if(use_nccl) {
         // reduce-scatter in place, Adam on the local shard, all-gather, flag sum
@@ -760,8 +955,7 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
         float *wf = arena_ptr<float>(h->arena, h->off_wf);
         float *gf = arena_ptr<float>(h->arena, h->off_gf);
         Ctrl *ctrl = arena_ptr<Ctrl>(h->arena, 0);
-        int rc = nccl_path_reduce_scatter(h->nccl, gh, h->sh, gf, h->sf, st,
-                                          &err);
+        rc = nccl_path_reduce_scatter(h->nccl, gh, h->sh, gf, h->sf, st, &err);
         if(rc)
             return fail(h, rc, err.c_str());
         // one-rank view of this rank's own memory: the shard now holds the sum
@@ -780,9 +974,10 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
         p.f.W[0] = wf;
         p.f.G[0] = gf;
         p.host = nullptr;
+        p.timing = 0;
         p.flags_dev = ctrl->coll_flags;
         p.barrier = 0;
-        CK(h, launch_step(p, 1, h->num_sms, tuning_of(h), st));
+        CK(h, launch_step(p, 1, h->num_sms, tune, st));
         rc = nccl_path_all_gather_and_flags(h->nccl, wh, h->sh, wf, h->sf,
                                             ctrl->coll_flags, st, &err);
         if(rc)
@@ -796,42 +991,18 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
     fill_groups(h, p, range);
     p.partial = last ? 0 : 1;
     p.barrier = (h->nranks > 1 && !h->serial) ? 1 : 0;
-    if(h->path == B200OPT_PATH_PUSH && h->nranks > 1) {
-        // 1. write this rank's contributions into the owners' staging slots
-        PushParams pp;
-        memset(&pp, 0, sizeof(pp));
-        pp.Gh = arena_ptr<uint16_t>(h->arena, h->off_gh);
-        pp.Gf = arena_ptr<float>(h->arena, h->off_gf);
-        pp.sh = h->sh;
-        pp.sf = h->sf;
-        pp.rank = h->rank;
-        pp.nranks = h->nranks;
-        pp.epoch = p.epoch;
-        for(int q = 0; q < h->nranks; q++) {
-            char *base = h->peer_arena[q];
-            pp.ctrl[q] = arena_ptr<Ctrl>(base, 0);
-            const size_t Aq = (h->sh * q) & ~(size_t)(kStateAlign - 1);
-            const size_t Afq = (h->sf * q) & ~(size_t)(kStateAlign - 1);
-            pp.Sh[q] = arena_ptr<uint16_t>(base, h->off_sh + h->slot_h_bytes * h->rank) - Aq;
-            pp.Sf[q] = arena_ptr<float>(base, h->off_sf + h->slot_f_bytes * h->rank) - Afq;
-        }
-        const size_t bytes = (h->sh * 2 + h->sf * 4) * (size_t)(h->nranks - 1);
-        const size_t per_cta = (size_t)kPushThreads * kPushUnroll * 16;
-        const int pgrid = (int)std::min<size_t>(std::max<size_t>(bytes / per_cta, 1),
-                                                (size_t)h->num_sms * 4);
-        push_grads_kernel<<<pgrid, kPushThreads, 0, st>>>(pp);
-        CK(h, cudaGetLastError());
-        h->launches++;
-        // 2. the step kernel sums its own shard with the staged ones: local loads
-        for(int q = 0; q < h->nranks; q++) {
-            if(q == h->rank)
-                continue;
-            p.h.G[q] = arena_ptr<uint16_t>(h->arena, h->off_sh + h->slot_h_bytes * q) - h->Ah;
-            p.f.G[q] = arena_ptr<float>(h->arena, h->off_sf + h->slot_f_bytes * q) - h->Af;
-        }
-        p.no_announce = 1;
+    if(tune.nvls) {
+        p.mcG = reinterpret_cast<const uint16_t *>(h->mc.va + h->off_gh);
+        p.mcW = reinterpret_cast<uint16_t *>(h->mc.va + h->off_wh);
     }
-    CK(h, launch_step(p, h->nranks, h->num_sms, tuning_of(h), st));
+    const cudaError_t ce = launch_step(p, h->nranks, h->num_sms, tune, st);
+    if(ce != cudaSuccess) {
+        // nothing was enqueued: stay in step with the peers
+        --h->epoch;
+        if(begins)
+            --h->iter;
+        return fail(h, B200OPT_ECUDA, "launch of the step kernel", ce);
+    }
     h->launches++;
     return B200OPT_OK;
 }
@@ -1188,6 +1359,7 @@ int b200opt_adam_mixed_static(size_t n, float alpha, void *weights,
     p.timeout_ns = 10000000000ull;
     p.ctrl[0] = ctrl;        // the fixed array, not an allocation
     p.flags_dev = flags_out;  // written by the last CTA, also when n == 0
+    p.flags_dev_status = 1;   // a wait that ran out shows as 0xFFFFFFFF there
     return launch_step(p, 1, sms, seam_tuning(), st) == cudaSuccess
                ? B200OPT_OK
                : B200OPT_ECUDA;
@@ -1285,7 +1457,7 @@ int b200opt_set_option(b200opt_t *h, int option, long value)
         h->timeout_ms = value;
         return B200OPT_OK;
     case B200OPT_OPT_PATH:
-        if(value < B200OPT_PATH_AUTO || value > B200OPT_PATH_PUSH)
+        if(value < B200OPT_PATH_AUTO || value > B200OPT_PATH_NVLS)
             return B200OPT_EINVAL;
         h->path = value;
         return B200OPT_OK;
@@ -1295,7 +1467,7 @@ int b200opt_set_option(b200opt_t *h, int option, long value)
         h->ctas_per_sm = value;
         return B200OPT_OK;
     case B200OPT_OPT_KERNEL_VARIANT:
-        if(value < 0 || value > 10)
+        if(value < 0 || value > 2)
             return B200OPT_EINVAL;
         h->variant = value;
         return B200OPT_OK;
@@ -1314,10 +1486,13 @@ int b200opt_set_option(b200opt_t *h, int option, long value)
             return B200OPT_EINVAL;
         h->grid = value;
         return B200OPT_OK;
-    case B200OPT_OPT_L2_HINT:
-        if(value < 0 || value > 3)
-            return B200OPT_EINVAL;
-        h->l2_hint = value;
+    case B200OPT_OPT_PHASE_TIMERS:
+        h->timing = value != 0;
+        return B200OPT_OK;
+    case B200OPT_OPT_ASSUME_NO_PEER_ACCESS:
+        if(h->peers_attached > 1)
+            return fail(h, B200OPT_ESTATE, "set before any peer is attached");
+        h->assume_no_peer_access = value != 0;
         return B200OPT_OK;
     }
     return B200OPT_EINVAL;
@@ -1335,9 +1510,23 @@ int b200opt_get_option(const b200opt_t *h, int option, long *value)
     case B200OPT_OPT_NCCL_CROSSOVER: *value = h->nccl_crossover; return B200OPT_OK;
     case B200OPT_OPT_STAGES: *value = h->stages; return B200OPT_OK;
     case B200OPT_OPT_GRID: *value = h->grid; return B200OPT_OK;
-    case B200OPT_OPT_L2_HINT: *value = h->l2_hint; return B200OPT_OK;
+    case B200OPT_OPT_PHASE_TIMERS: *value = h->timing; return B200OPT_OK;
+    case B200OPT_OPT_ASSUME_NO_PEER_ACCESS:
+        *value = h->assume_no_peer_access;
+        return B200OPT_OK;
     }
     return B200OPT_EINVAL;
+}
+
+int b200opt_phase_times(const b200opt_t *h, uint64_t ns_out[4])
+{
+    if(!h || !ns_out)
+        return B200OPT_EINVAL;
+    if(!h->timing)
+        return B200OPT_ESTATE;
+    for(int k = 0; k < 4; k++)
+        ns_out[k] = h->host->phase_ns[k];
+    return B200OPT_OK;
 }
 
 int b200opt_launch_count(const b200opt_t *h, uint64_t *launches)

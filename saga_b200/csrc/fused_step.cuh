@@ -51,7 +51,7 @@ struct alignas(128) Ctrl {
     uint32_t cta_done;         // CTAs of the running launch that finished
     uint32_t local_flags;      // OR of this rank's flag bits
     uint32_t status;           // sticky B200OPT_E* (as positive number) or 0
-    uint32_t push_done;        // CTAs of the running gradient-push launch that finished
+    uint32_t reserved0;
     uint32_t coll_flags[4];    // NCCL path: {range, inf, nan} to be all-reduced
     // device-resident loss scale (optional): updated by the last CTA of a step
     float scale;               // current loss scale
@@ -59,8 +59,14 @@ struct alignas(128) Ctrl {
     int32_t clean_steps;       // interval policy: clean steps since the last change
     int32_t interval;          // interval policy: growth interval
     uint32_t log_pos;          // steps logged so far
-    uint32_t pad[19];
+    uint32_t reserved1;
+    // phase timers (optional): %globaltimer at kernel entry and the time CTA 0
+    // spent waiting for the peers' announcements
+    unsigned long long t_start;
+    unsigned long long t_entry_wait;
+    uint32_t pad[14];
 };
+static_assert(sizeof(Ctrl) == 640, "control block layout");
 
 // Written by the last CTA of a launch, read by the host after a stream sync.
 struct HostResult {
@@ -70,6 +76,11 @@ struct HostResult {
     uint32_t where;   // 1 = wait for gradients, 2 = wait for completion
     uint32_t peer;    // rank that did not arrive
     uint32_t pad;
+    // phase timers of the last launch, nanoseconds of %globaltimer (only with
+    // B200OPT_OPT_PHASE_TIMERS): wait for the peers' announcements in CTA 0,
+    // kernel entry until the last CTA finished its share, the completion
+    // protocol in the last CTA, and kernel entry until the end of it
+    unsigned long long phase_ns[4];
 };
 
 struct HalfGroup {
@@ -98,9 +109,6 @@ struct StepParams {
     int barrier;      // 1: wait for peers inside the kernel
     int force_scalar; // 1: pointers are not 16-byte aligned, element-wise path
     int stages;       // staged kernel: depth of the shared-memory ring
-    int l2_hint;      // staged kernel: bit 0 loads, bit 1 stores carry an L2 evict-first hint
-    int no_announce;  // 1: the gradient-push kernel has already told the peers that
-                      // this rank's contributions are in place
     int partial;      // 1: a bucket of a step that is not its last (no completion
                       // protocol across ranks, flags keep accumulating)
     uint32_t epoch;
@@ -109,10 +117,17 @@ struct StepParams {
     HostResult *host;       // pinned, may be null
     uint32_t *aux;          // kernel-seam mode: store 1 into aux[0..2], no ctrl
     uint32_t *flags_dev;    // NCCL path: this rank's {range, inf, nan} as 0/1
+    int flags_dev_status;   // 1: a wait that ran out is reported as 0xFFFFFFFF in
+                            // all three words of flags_dev (no host page to carry it)
     int device_scale;       // 1: 1/scale comes from ctrl[rank]->scale, and the last
                             // CTA applies the loss-scale policy to it
     uint32_t *scale_log;    // ring of {range, inf, nan, bits of the new scale} per step
     uint32_t scale_log_cap; // entries in the ring (0: no log)
+    int timing;             // 1: record the phase timers
+    // multicast views of the fp16 gradient and weight buffers of all ranks
+    // (switch-reduced loads, switch-replicated stores); null off that path
+    const uint16_t *mcG;
+    uint16_t *mcW;
 };
 
 // 1/scale of this step: from the launch arguments, or from the scale that
@@ -585,11 +600,21 @@ __device__ __noinline__ uint32_t float_scalar(const StepParams &p, size_t idx0)
 template <int NR>
 __device__ __forceinline__ int step_begin(const StepParams &p)
 {
-    if(NR == 1 || !p.barrier)
+    if(NR == 1 || !p.barrier) {
+        if(p.timing && blockIdx.x == 0 && threadIdx.x == 0 && p.ctrl[p.rank]) {
+            p.ctrl[p.rank]->t_start = globaltimer_ns();
+            p.ctrl[p.rank]->t_entry_wait = 0;
+        }
         return 0;
+    }
     const int tid = threadIdx.x;
     Ctrl *const my = p.ctrl[p.rank];
-    if(blockIdx.x == 0 && tid < NR && !p.no_announce)
+    unsigned long long t0 = 0;
+    if(p.timing && blockIdx.x == 0 && tid == 0) {
+        t0 = globaltimer_ns();
+        my->t_start = t0;
+    }
+    if(blockIdx.x == 0 && tid < NR)
         st_release_sys(&p.ctrl[tid]->ready[p.rank], p.epoch);
     int bad = 0;
     if(tid < NR) {
@@ -602,7 +627,10 @@ __device__ __forceinline__ int step_begin(const StepParams &p)
             }
         }
     }
-    return __syncthreads_or(bad);
+    bad = __syncthreads_or(bad);
+    if(p.timing && blockIdx.x == 0 && tid == 0)
+        my->t_entry_wait = globaltimer_ns() - t0;
+    return bad;
 }
 
 // The fp32 group (BatchNorm scales and biases in an fp16 network: a few tens
@@ -682,6 +710,7 @@ __device__ __forceinline__ void step_finish(const StepParams &p, uint32_t fl,
         return;
     }
 
+    const unsigned long long t_body = p.timing ? globaltimer_ns() : 0;
     const uint32_t mine =
         *reinterpret_cast<volatile uint32_t *>(&my->local_flags);
     uint32_t status = *reinterpret_cast<volatile uint32_t *>(&my->status);
@@ -727,9 +756,10 @@ __device__ __forceinline__ void step_finish(const StepParams &p, uint32_t fl,
         if(p.device_scale && !status)
             device_scale_update(p, my, sums);
         if(p.flags_dev) {
-            p.flags_dev[0] = sums[0];
-            p.flags_dev[1] = sums[1];
-            p.flags_dev[2] = sums[2];
+            const bool gave_up = p.flags_dev_status && status;
+            p.flags_dev[0] = gave_up ? 0xFFFFFFFFu : sums[0];
+            p.flags_dev[1] = gave_up ? 0xFFFFFFFFu : sums[1];
+            p.flags_dev[2] = gave_up ? 0xFFFFFFFFu : sums[2];
         }
         if(p.host) {
             p.host->range = sums[0];
@@ -737,6 +767,16 @@ __device__ __forceinline__ void step_finish(const StepParams &p, uint32_t fl,
             p.host->nan = sums[2];
             p.host->status = status;
             p.host->epoch = p.epoch;
+            if(p.timing) {
+                const unsigned long long t_end = globaltimer_ns();
+                const unsigned long long t_start =
+                    *reinterpret_cast<volatile unsigned long long *>(&my->t_start);
+                p.host->phase_ns[0] =
+                    *reinterpret_cast<volatile unsigned long long *>(&my->t_entry_wait);
+                p.host->phase_ns[1] = t_body - t_start;
+                p.host->phase_ns[2] = t_end - t_body;
+                p.host->phase_ns[3] = t_end - t_start;
+            }
         }
         my->local_flags = 0;
         my->cta_done = 0;

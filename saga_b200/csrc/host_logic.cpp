@@ -71,4 +71,53 @@ int b200opt_layout(const size_t *sizes, size_t k, size_t *offsets,
     return B200OPT_OK;
 }
 
+// Which collective path a step takes.  Kept free of CUDA so that the rule can
+// be checked on a machine without a GPU.
+int b200opt_choose_path(int requested, int nranks, int serial,
+                        int peers_reachable, int have_nccl, int have_multicast,
+                        size_t n_half, size_t nccl_crossover, int *chosen)
+{
+    if(!chosen || nranks < 1 || requested < B200OPT_PATH_AUTO ||
+       requested > B200OPT_PATH_NVLS)
+        return B200OPT_EINVAL;
+    // one rank, or several ranks stepped one after the other on one GPU: the
+    // peer-pointer kernel is the only arithmetic there is
+    if(nranks == 1 || serial) {
+        if(requested == B200OPT_PATH_NVLS && nranks > 1)
+            return B200OPT_EUNSUPPORTED;
+        *chosen = B200OPT_PATH_PEER;
+        return B200OPT_OK;
+    }
+    switch(requested) {
+    case B200OPT_PATH_NCCL:
+        if(!have_nccl)
+            return B200OPT_ESTATE;
+        *chosen = B200OPT_PATH_NCCL;
+        return B200OPT_OK;
+    case B200OPT_PATH_NVLS:
+        if(!have_multicast)
+            return B200OPT_ESTATE;
+        *chosen = B200OPT_PATH_NVLS;
+        return B200OPT_OK;
+    case B200OPT_PATH_PEER:
+        if(!peers_reachable)
+            return B200OPT_EUNSUPPORTED;
+        *chosen = B200OPT_PATH_PEER;
+        return B200OPT_OK;
+    }
+    // AUTO: the peer-pointer kernel (bit for bit the rank-ordered sum) unless
+    // the GPUs cannot reach one another's memory or the buffer is below the
+    // size at which NCCL was measured to win; never the multicast path, whose
+    // sum order is the switch's
+    if(!peers_reachable) {
+        if(!have_nccl)
+            return B200OPT_EUNSUPPORTED;
+        *chosen = B200OPT_PATH_NCCL;
+        return B200OPT_OK;
+    }
+    *chosen = (have_nccl && n_half < nccl_crossover) ? B200OPT_PATH_NCCL
+                                                     : B200OPT_PATH_PEER;
+    return B200OPT_OK;
+}
+
 }  // extern "C"

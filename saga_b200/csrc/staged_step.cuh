@@ -81,33 +81,6 @@ __device__ __forceinline__ void bulk_store(void *gdst, const void *smem_src,
                  "r"(smem_u32(smem_src)), "r"(bytes)
                  : "memory");
 }
-// The same copies with an L2 eviction-priority hint: this path touches every
-// byte once per step, so its lines can leave L2 first.
-__device__ __forceinline__ uint64_t l2_evict_first_policy()
-{
-    uint64_t pol;
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-    return pol;
-}
-__device__ __forceinline__ void bulk_load_hint(void *smem_dst, const void *gsrc,
-                                               uint32_t bytes, uint64_t *bar,
-                                               uint64_t pol)
-{
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
-        "[%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(smem_dst)),
-        "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)), "l"(pol)
-        : "memory");
-}
-__device__ __forceinline__ void bulk_store_hint(void *gdst, const void *smem_src,
-                                                uint32_t bytes, uint64_t pol)
-{
-    asm volatile(
-        "cp.async.bulk.global.shared::cta.bulk_group.L2::cache_hint [%0], [%1], %2, %3;" ::
-            "l"(gdst),
-        "r"(smem_u32(smem_src)), "r"(bytes), "l"(pol)
-        : "memory");
-}
 __device__ __forceinline__ void bulk_commit()
 {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -263,7 +236,6 @@ __global__ void __launch_bounds__(THREADS)
     uint32_t fl = 0;
     if(!step_begin<NR>(p)) {
         const float alpha = step_alpha(p);
-        const uint64_t pol = l2_evict_first_policy();
         // full 8-element groups of the shard: [F0, F1); the (at most two)
         // ragged groups at the shard's ends go through the element-wise path
         const size_t lo = p.h.o, hi = p.h.o + p.h.s;
@@ -297,16 +269,6 @@ __global__ void __launch_bounds__(THREADS)
             const uint32_t te = tile_elems(k);
             unsigned char *st = stage_mem + (size_t)s * kStage;
             mbar_expect_tx(&full_bar[s], te * (2u * NR + 12u));
-            if(p.l2_hint & 1) {
-#pragma unroll
-                for(int q = 0; q < NR; q++)
-                    bulk_load_hint(st + q * TILE * 2, p.h.G[q] + e0, te * 2u,
-                                   &full_bar[s], pol);
-                bulk_load_hint(st + kOffM, p.h.m + l0, te * 4u, &full_bar[s], pol);
-                bulk_load_hint(st + kOffV, p.h.v + l0, te * 4u, &full_bar[s], pol);
-                bulk_load_hint(st + kOffC, p.h.c + l0, te * 4u, &full_bar[s], pol);
-                return;
-            }
 #pragma unroll
             for(int q = 0; q < NR; q++)
                 bulk_load(st + q * TILE * 2, p.h.G[q] + e0, te * 2u,
@@ -345,21 +307,12 @@ __global__ void __launch_bounds__(THREADS)
             __syncthreads();
             if(tid == 0) {
                 const size_t l0 = e0 - p.h.A;
-                if(p.l2_hint & 2) {
-                    bulk_store_hint(p.h.m + l0, st + kOffM, te * 4u, pol);
-                    bulk_store_hint(p.h.v + l0, st + kOffV, te * 4u, pol);
-                    bulk_store_hint(p.h.c + l0, st + kOffC, te * 4u, pol);
+                bulk_store(p.h.m + l0, st + kOffM, te * 4u);
+                bulk_store(p.h.v + l0, st + kOffV, te * 4u);
+                bulk_store(p.h.c + l0, st + kOffC, te * 4u);
 #pragma unroll
-                    for(int q = 0; q < NR; q++)
-                        bulk_store_hint(p.h.W[q] + e0, st, te * 2u, pol);
-                } else {
-                    bulk_store(p.h.m + l0, st + kOffM, te * 4u);
-                    bulk_store(p.h.v + l0, st + kOffV, te * 4u);
-                    bulk_store(p.h.c + l0, st + kOffC, te * 4u);
-#pragma unroll
-                    for(int q = 0; q < NR; q++)
-                        bulk_store(p.h.W[q] + e0, st, te * 2u);
-                }
+                for(int q = 0; q < NR; q++)
+                    bulk_store(p.h.W[q] + e0, st, te * 2u);
                 bulk_commit();
                 // refill the stage whose stores were issued one trip ago
                 if(STAGES > 1 && k >= 1 && k - 1 + STAGES < nmine) {

@@ -1,12 +1,15 @@
 """Builds the two end-to-end training binaries (needs the Saga checkout):
 
-  oracle/_ref/saga_e2e_ref    the reference library, unmodified (NCCL build),
-                              + its own test/test_classifier.cpp + e2e_main.cpp
-  oracle/_ref/saga_cifar18_*  the same two library builds + e2e_cifar_resnet18.cpp
-  oracle/_ref/saga_e2e_b200   the same with the optimizer ops replaced by the
-                              b200opt op: the library sources are copied to a
-                              scratch directory outside this repository and
-                              edited there by the small anchored rewrites below
+  _build/saga_e2e_ref    the reference library, unmodified (NCCL build),
+                         + its own test/test_classifier.cpp + e2e_main.cpp
+  _build/saga_cifar18_*  the same two library builds + e2e_cifar_resnet18.cpp
+  _build/saga_e2e_b200   the same with the optimizer ops replaced by the
+                         b200opt op: the library sources are copied to a
+                         scratch directory outside this repository and
+                         edited there by the small anchored rewrites below
+
+(_build/ is this file's sibling directory.)  The checkout is the first argument,
+else $SAGA_REFERENCE_DIR, else a directory "reference" beside this repository.
 
     python saga_b200/host/e2e/build_saga_e2e.py [/path/to/saga]
 
@@ -21,7 +24,7 @@ import tempfile
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.abspath(os.path.join(HERE, "..", "..", ".."))
-OUT = os.path.join(ROOT, "oracle", "_ref")
+OUT = os.path.join(HERE, "_build")
 
 LIB_SRCS = ["src/util.cpp", "src/tensor.cpp", "src/graph.cpp", "src/node.cpp", "src/engine.cpp",
             "src/ui/tui.cpp", "src/ui/nui.cpp", "src/pub.cpp",
@@ -118,7 +121,8 @@ def build_variant(ref, work, name, defines, extra_inc, extra_libs):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = (sys.argv[1] if len(sys.argv) > 1 else
+           os.environ.get("SAGA_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference"))
     if not os.path.exists(os.path.join(ref, "saga.hpp")):
         print(f"Saga checkout not found at {ref}: keeping any prebuilt binaries")
         return
@@ -133,7 +137,7 @@ def main():
         print(build_variant(tree, work, "saga_e2e_b200", ["-DHAVE_B200OPT"],
                             ["-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(ROOT, "saga_b200", "host"),
                              "-I" + HERE],
-                            ["-L" + libdir, "-lb200opt", "-Wl,-rpath,$ORIGIN/../../saga_b200"]))
+                            ["-L" + libdir, "-lb200opt", "-Wl,-rpath,$ORIGIN/../../.."]))
     finally:
         shutil.rmtree(work, ignore_errors=True)
 

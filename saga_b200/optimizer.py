@@ -84,25 +84,39 @@ class AdamGroup:
 
     def __init__(self, handle, rank, nranks, device, n_half, n_float, owns=True):
         self._h = C.c_void_p(handle)
+        self.flags_created = 0
         self.rank, self.nranks, self.device = rank, nranks, device
         self.n_half, self.n_float = int(n_half), int(n_float)
         self._owns = owns
 
     # ------------------------------------------------------------ creation
     @classmethod
-    def create(cls, rank, nranks, device, n_half, n_float=0):
+    def create(cls, rank, nranks, device, n_half, n_float=0, flags=0):
+        """One rank; flags = capi.CREATE_FABRIC / capi.CREATE_MULTICAST for an arena that is
+        shared by file descriptor and can be bound to an NVSwitch multicast object."""
         h = C.c_void_p()
-        check(lib().b200opt_create(C.byref(h), rank, nranks, device, n_half, n_float))
-        return cls(h.value, rank, nranks, device, n_half, n_float)
+        check(lib().b200opt_create_ex(C.byref(h), rank, nranks, device, n_half, n_float, flags))
+        g = cls(h.value, rank, nranks, device, n_half, n_float)
+        g.flags_created = flags
+        return g
 
     @classmethod
-    def create_group(cls, devices, n_half, n_float=0):
+    def create_group(cls, devices, n_half, n_float=0, flags=0):
         """All ranks in this process, wired to one another (Saga's threading model)."""
         n = len(devices)
         hs = (C.c_void_p * n)()
         devs = (C.c_int * n)(*devices)
-        check(lib().b200opt_create_group(hs, n, devs, n_half, n_float))
-        return [cls(hs[r], r, n, devices[r], n_half, n_float) for r in range(n)]
+        check(lib().b200opt_create_group_ex(hs, n, devs, n_half, n_float, flags))
+        out = [cls(hs[r], r, n, devices[r], n_half, n_float) for r in range(n)]
+        for g in out:
+            g.flags_created = flags
+        return out
+
+    @staticmethod
+    def multicast_supported(device):
+        yes = C.c_int()
+        check(lib().b200opt_multicast_supported(device, C.byref(yes)))
+        return bool(yes.value)
 
     def destroy(self):
         if self._h and self._owns:
@@ -128,6 +142,27 @@ class AdamGroup:
     def ipc_attach(self, peer_rank, handle_bytes):
         buf = (C.c_ubyte * capi.IPC_HANDLE_BYTES).from_buffer_copy(handle_bytes)
         check(lib().b200opt_ipc_attach(self._h, peer_rank, buf), self._h)
+
+    def fd_export(self):
+        """File descriptor of this rank's arena (CREATE_FABRIC); the caller closes it."""
+        fd = C.c_int(-1)
+        check(lib().b200opt_fd_export(self._h, C.byref(fd)), self._h)
+        return fd.value
+
+    def fd_attach(self, peer_rank, fd):
+        check(lib().b200opt_fd_attach(self._h, peer_rank, fd), self._h)
+
+    def mc_create(self):
+        """Rank 0: creates the multicast object; returns its descriptor for the other ranks."""
+        fd = C.c_int(-1)
+        check(lib().b200opt_mc_create(self._h, C.byref(fd)), self._h)
+        return fd.value
+
+    def mc_join(self, fd):
+        check(lib().b200opt_mc_join(self._h, fd), self._h)
+
+    def mc_bind(self):
+        check(lib().b200opt_mc_bind(self._h), self._h)
 
     def nccl_init(self, unique_id):
         buf = (C.c_ubyte * capi.NCCL_ID_BYTES).from_buffer_copy(unique_id)
@@ -247,6 +282,13 @@ class AdamGroup:
         v = C.c_long()
         check(lib().b200opt_get_option(self._h, option, C.byref(v)), self._h)
         return v.value
+
+    def phase_times(self):
+        """(entry wait, entry..last CTA done, completion protocol, total) of the last step
+        kernel in ns; needs OPT_PHASE_TIMERS and a preceding flags()."""
+        out = (C.c_uint64 * 4)()
+        check(lib().b200opt_phase_times(self._h, out), self._h)
+        return tuple(int(x) for x in out)
 
     @property
     def launch_count(self):

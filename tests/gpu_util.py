@@ -24,12 +24,13 @@ def stream_ptr(device=0):
 class Program:
     """N ranks of the CUDA path with the weights/gradients API the tests need."""
 
-    def __init__(self, nranks, n_half, n_float=0, devices=None, variant=None, path=None):
+    def __init__(self, nranks, n_half, n_float=0, devices=None, variant=None, path=None,
+                 create_flags=0):
         devices = devices or [0] * nranks
         self.N = nranks
         self.devices = devices
-        self.groups = (AdamGroup.create_group(devices, n_half, n_float) if nranks > 1
-                       else [AdamGroup.create(0, 1, devices[0], n_half, n_float)])
+        self.groups = (AdamGroup.create_group(devices, n_half, n_float, create_flags) if nranks > 1
+                       else [AdamGroup.create(0, 1, devices[0], n_half, n_float, create_flags)])
         self.Wh, self.Gh, self.Wf, self.Gf = [], [], [], []
         for g in self.groups:
             if variant is not None:

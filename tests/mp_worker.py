@@ -49,6 +49,23 @@ def run_gloo(out_path):
     assert launch.max_over_ranks([1.0 + rank, 5.0 - rank]) == [float(world), 5.0]
     assert launch.broadcast_bytes(b"id-from-0" if rank == 0 else b"", 0) == b"id-from-0"
 
+    # file descriptors between ranks: every rank sends the write end of a pipe to every
+    # other rank, which writes its own rank number into it
+    ex = launch.FdExchange(rank, world)
+    rd, wr = os.pipe()
+    for q in range(world):
+        if q != rank:
+            ex.send(q, wr, 40 + rank)
+    os.close(wr)
+    for src, tag, fd in ex.recv(world - 1):
+        assert tag == 40 + src
+        os.write(fd, bytes([rank]))
+        os.close(fd)
+    dist.barrier()
+    assert sorted(os.read(rd, 64)) == [q for q in range(world) if q != rank]
+    os.close(rd)
+    ex.close()
+
     # each rank owns only its gradients; the reduction needs everyone's
     n, steps = 4096, 12
     W0 = synth.weights_half(n, seed=5)
@@ -82,10 +99,20 @@ def run_gpu(out_path, path="peer"):
     torch.cuda.set_device(dev)
     dist.init_process_group("cpu:gloo,cuda:nccl", device_id=dev)
     n_half, n_float, steps = 2048 * 6 * world + 80, 528, 8
-    grp = AdamGroup.create(rank, world, local, n_half, n_float)
+    flags = {"fabric": capi.CREATE_FABRIC, "nvls": capi.CREATE_MULTICAST}.get(path, 0)
+    grp = AdamGroup.create(rank, world, local, n_half, n_float, flags)
     grp.set_option(capi.OPT_TIMEOUT_MS, 20000)
-    launch.wire_process_group(grp, with_nccl=(path == "nccl"))
-    grp.set_option(capi.OPT_PATH, {"nccl": capi.PATH_NCCL, "push": capi.PATH_PUSH}.get(path, capi.PATH_PEER))
+    info = launch.wire_process_group(grp, with_nccl=(path == "nccl"))
+    if path == "nvls" and not info["multicast"]:
+        if rank == 0:
+            with open(out_path, "w") as f:
+                json.dump({"ok": True, "path": path, "ranks": [],
+                           "skipped": "these GPUs do not support NVSwitch multicast"}, f)
+        dist.barrier()
+        grp.destroy()
+        dist.destroy_process_group()
+        return
+    grp.set_option(capi.OPT_PATH, {"nccl": capi.PATH_NCCL, "nvls": capi.PATH_NVLS}.get(path, capi.PATH_PEER))
     sp = torch.cuda.current_stream(dev).cuda_stream
     W0, Wf0 = synth.weights_half(n_half, seed=9), synth.weights_float(n_float, seed=9)
     w, g = grp.buffers(capi.HALF)
@@ -132,6 +159,7 @@ def run_gpu(out_path, path="peer"):
     if rank == 0:
         with open(out_path, "w") as f:
             json.dump({"ok": True, "path": path, "ranks": res}, f)
+    dist.barrier()   # every rank has finished stepping before any arena is released
     grp.destroy()
     dist.destroy_process_group()
 

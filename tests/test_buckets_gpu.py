@@ -78,7 +78,7 @@ def _same(a, b):
         assert np.array_equal(a[k].view(np.uint8), b[k].view(np.uint8)), k
 
 
-@pytest.mark.parametrize("variant", [None, 1, 2, 7])
+@pytest.mark.parametrize("variant", [None, 1, 2])
 @pytest.mark.parametrize("nranks", [1, 2, 4])
 def test_bucketed_step_equals_whole_step(nranks, variant):
     for n_half, n_float in ((2048 * 5 * nranks + 48, 1040), (272, 0)):

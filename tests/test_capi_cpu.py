@@ -99,3 +99,39 @@ def test_header_is_plain_c(tmp_path):
                           "-I", os.path.join(ROOT, "include"), str(src)],
                          capture_output=True, text=True)
     assert res.returncode == 0, res.stderr
+
+
+def test_path_rule(built_library):
+    """Which collective path a step takes, including the fallback to NCCL when the
+    GPUs cannot reach one another's memory (no GPU needed: the rule is host-only)."""
+    from saga_b200 import capi
+    L = capi.lib()
+
+    def choose(req, nranks=8, serial=0, reach=1, nccl=0, mc=0, n=1 << 20, cross=0):
+        out = C.c_int(-1)
+        rc = L.b200opt_choose_path(req, nranks, serial, reach, nccl, mc, n, cross, C.byref(out))
+        return rc, out.value
+
+    A, P, N, M = capi.PATH_AUTO, capi.PATH_PEER, capi.PATH_NCCL, capi.PATH_NVLS
+    # default: the bit-exact peer kernel, never the multicast path by itself
+    assert choose(A) == (capi.OK, P)
+    assert choose(A, nccl=1, mc=1) == (capi.OK, P)
+    # no peer access: NCCL by itself; nothing usable without a communicator
+    assert choose(A, reach=0, nccl=1) == (capi.OK, N)
+    assert choose(A, reach=0, nccl=0)[0] == capi.EUNSUPPORTED
+    assert choose(P, reach=0, nccl=1)[0] == capi.EUNSUPPORTED
+    # measured crossover: NCCL only below it and only with a communicator
+    assert choose(A, nccl=1, n=1000, cross=4096) == (capi.OK, N)
+    assert choose(A, nccl=0, n=1000, cross=4096) == (capi.OK, P)
+    assert choose(A, nccl=1, n=8192, cross=4096) == (capi.OK, P)
+    # explicit requests need what they run on
+    assert choose(N, nccl=0)[0] == capi.ESTATE
+    assert choose(N, nccl=1) == (capi.OK, N)
+    assert choose(M, mc=0)[0] == capi.ESTATE
+    assert choose(M, mc=1) == (capi.OK, M)
+    # one rank, or ranks stepped serially on one GPU: always the peer-pointer kernel
+    assert choose(N, nranks=1, nccl=1) == (capi.OK, P)
+    assert choose(A, nranks=4, serial=1, reach=0) == (capi.OK, P)
+    assert choose(M, nranks=4, serial=1, mc=1)[0] == capi.EUNSUPPORTED
+    assert choose(7)[0] == capi.EINVAL
+    assert L.b200opt_choose_path(A, 2, 0, 1, 0, 0, 16, 0, None) == capi.EINVAL

@@ -9,7 +9,7 @@ import shutil
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.environ.get("SAGA_CHECKOUT", "/root/reference")
+REF = os.environ.get("SAGA_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
 
 
 def _load():

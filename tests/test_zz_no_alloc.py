@@ -84,6 +84,38 @@ def test_static_entry_point_matches_adam_mixed_on_two_calls_in_a_row(oracle, n):
     assert np.array_equal(host_u16(b["w"]), ow)
 
 
+def test_static_entry_point_allocates_nothing_and_accepts_an_empty_buffer(oracle):
+    """After the first call on the device (which looks up the scratch array and opts the
+    kernel in to its shared-memory size), further calls leave the amount of free device
+    memory exactly where it was; n = 0 still reports (zero) flags; and a clean call after
+    a flagged one does not inherit its flags from the shared scratch."""
+    n = 1 << 16
+    w0 = synth.weights_half(n, seed=78)
+    t = dict(w=dev_u16(w0), c=dev_f32(oracle.master_init(w0)), m=torch.zeros(n, device="cuda"),
+             v=torch.zeros(n, device="cuda"))
+    flags = torch.full((3,), 9, dtype=torch.int32, device="cuda")
+    clean = dev_u16(synth.grads_half(n, 64.0, 1, seed=78))
+    bad_bits = synth.grads_half(n, 64.0, 2, seed=78)
+    bad_bits[11] = 0x7E01          # NaN
+    bad = dev_u16(bad_bits)
+    b1t, b2t = oracle.bias_corrections(1)
+    _call_static(n, oracle.alpha(64.0), t, clean, b1t, b2t, 1e-3, 0.0, flags)   # set-up call
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    _call_static(n, oracle.alpha(64.0), t, bad, b1t, b2t, 1e-3, 0.0, flags)
+    torch.cuda.synchronize()
+    assert tuple(int(x) for x in flags.cpu()) == (1, 0, 1)
+    _call_static(n, oracle.alpha(64.0), t, clean, b1t, b2t, 1e-3, 0.0, flags)
+    torch.cuda.synchronize()
+    assert tuple(int(x) for x in flags.cpu()) == (0, 0, 0)      # nothing left over
+    flags.fill_(9)
+    _call_static(0, oracle.alpha(64.0), t, clean, b1t, b2t, 1e-3, 0.0, flags)
+    torch.cuda.synchronize()
+    assert tuple(int(x) for x in flags.cpu()) == (0, 0, 0)      # written also for n = 0
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, "the allocation-free entry point changed the free device memory"
+
+
 def test_static_entry_point_rejects_sizes_beyond_its_scratch():
     vp = C.c_void_p
     flags = torch.zeros(3, dtype=torch.int32, device="cuda")
