@@ -371,17 +371,40 @@ def set_path(grp, path):
                                        "nccl": capi.PATH_NCCL}[path])
 
 
-def timed_steps(env, fn, k):
+def timed_steps(env, fn, k, lead_in=3):
     """k calls of fn back to back on the stream with one event between every two;
-    returns the per-step device times in ms (this rank)."""
+    returns the per-step device times in ms (this rank) and their total.
+
+    `lead_in` untimed calls are enqueued first, in the same burst: the ranks leave the
+    host barrier tens of microseconds apart, and without work already queued on every
+    GPU that host-side skew would sit inside the first timed step (the slowest rank's
+    late launch stalls everyone in the step's entry wait).  The first event is recorded
+    on the stream behind the lead-in, whose completion protocol aligns the GPUs."""
     torch = env.torch
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(k + 1)]
+    for _ in range(lead_in if env.world > 1 else 0):
+        fn()
     ev[0].record(env.stream)
     for i in range(k):
         fn()
         ev[i + 1].record(env.stream)
     torch.cuda.synchronize(env.dev)
     return [ev[i].elapsed_time(ev[i + 1]) for i in range(k)], ev[0].elapsed_time(ev[k])
+
+
+def timed_block(env, fn, k, lead_in=3):
+    """k calls of fn back to back between ONE pair of events (plus the untimed lead-in
+    described in timed_steps); device time in ms (this rank)."""
+    torch = env.torch
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(lead_in if env.world > 1 else 0):
+        fn()
+    a.record(env.stream)
+    for _ in range(k):
+        fn()
+    b.record(env.stream)
+    torch.cuda.synchronize(env.dev)
+    return a.elapsed_time(b)
 
 
 def summarize(per_step_ms):
@@ -394,17 +417,27 @@ def summarize(per_step_ms):
 
 def parity_leg(env, path):
     """A small buffer stepped through the real collective path of this run at this N
-    and compared with the CPU oracle (rank-ordered fp32 sum, the reference's update):
-    2048*6*N+80 fp16 + 528 fp32 parameters, 4 steps, an inf from rank 0 on step 2, a
-    32768 in two shards on step 3.  Returns the block for the JSON line."""
+    and compared with the CPU oracle (rank-ordered fp32 sum, one fp16 rounding, the
+    reference's update): 2048*6*N+80 fp16 + 528 fp32 parameters, 4 steps, an inf from
+    rank 0 on step 2, a 32768 in two shards on step 3.  Returns the block for the JSON line.
+
+    Peer path: everything bit for bit (reported as relative error and bit differences).
+    Multicast path: the switch forms the fp16 sum with its own arithmetic, so the check
+    has two parts -- the sums it returned (the kernel leaves them in the gradient buffer,
+    where ncclReduceScatter leaves them in Saga) lie within one fp16 ulp of the
+    rank-ordered sums, and GIVEN those sums flags, loss scale, m, v, master and weights
+    equal the oracle's bit for bit."""
     import torch
     from oracle import oracle as orc
     from saga_b200 import LossScaler, capi, workload
     N, rank = env.world, env.rank
     n_half, n_float, steps = 2048 * 6 * N + 80, 528, 4
     grp, used, _ = make_group(env, n_half, n_float, path)
+    nvls = used == "nvls"
     out = {"n_ranks": N, "path": used, "n_half": n_half, "n_float": n_float, "steps": steps}
     try:
+        if nvls:
+            grp.set_option(capi.OPT_KEEP_REDUCED, 1)
         W0, Wf0 = workload.weights_half(n_half, seed=17), workload.weights_float(n_float, seed=17)
         w, g = grp.buffers(capi.HALF)
         wf, gf = grp.buffers(capi.FLOAT)
@@ -417,6 +450,7 @@ def parity_leg(env, path):
         sh = n_half // N
         flags_equal = scale_equal = True
         flag_log = []
+        sum_ulp_max = sum_off = 0
         for step in range(1, steps + 1):
             G = [workload.grads_half(n_half, oscale, step, rank=r, seed=17) for r in range(N)]
             Gf = [workload.grads_float(n_float, oscale, step, rank=r, seed=17) for r in range(N)]
@@ -430,6 +464,16 @@ def parity_leg(env, path):
             env.barrier()
             grp.exec(1e-2, 0.01, scaler.scale, env.sp)
             flags = grp.flags(env.sp)
+            if nvls:
+                parts = [None] * N
+                env.dist.all_gather_object(
+                    parts, g[rank * sh:(rank + 1) * sh].view(torch.int16).cpu().numpy().tobytes())
+                reduced = G[0].copy()
+                reduced[:N * sh] = np.frombuffer(b"".join(parts), dtype=np.uint16)
+                d = orc.half_ulp_distance(reduced[:N * sh], orc.rank_ordered_sum_half(G)[:N * sh])
+                sum_ulp_max = max(sum_ulp_max, int(d.max()))
+                sum_off += int(np.count_nonzero(d))
+                G = [reduced] + [np.full(n_half, 0x8000, np.uint16) for _ in range(N - 1)]
             oflags = ost.step([x.copy() for x in G], [x.copy() for x in Gf], oscale, 1e-2, 0.01)
             flag_log.append(list(flags))
             flags_equal &= tuple(flags) == tuple(oflags)
@@ -453,16 +497,26 @@ def parity_leg(env, path):
             worst = max(worst, rel(grp.export_state(capi.FLOAT, which), ref))
         mine_w = w.view(torch.int16).cpu().numpy().view(np.uint16)
         d = np.abs(mine_w.astype(np.int64) - ost.W[0].astype(np.int64))
-        worst, ulp, wdiff, sdiff = env.max_over_ranks(
-            [worst, float(d.max()), float(np.count_nonzero(d)), float(state_bit_diffs)])
+        worst, ulp, wdiff, sdiff, sulp, soff = env.max_over_ranks(
+            [worst, float(d.max()), float(np.count_nonzero(d)), float(state_bit_diffs),
+             float(sum_ulp_max), float(sum_off)])
         all_flags = env.all_true(flags_equal)
         all_scale = env.all_true(scale_equal)
         out.update({"flags_equal": all_flags, "scale_bits_equal": all_scale,
                     "max_rel_err": worst, "w_ulp_max": int(ulp), "w_bit_diffs": int(wdiff),
-                    "state_bit_diffs_max_rank": int(sdiff), "flags_per_step": flag_log,
-                    "against": "CPU oracle: rank-ordered fp32 sum, one fp16 rounding, "
-                               "reference update; tolerance 1e-6 per step"})
-        out["ok"] = bool(all_flags and all_scale and worst <= 1e-6 * steps and ulp <= 1)
+                    "state_bit_diffs_max_rank": int(sdiff), "flags_per_step": flag_log})
+        if nvls:
+            out.update({
+                "switch_sum_ulp_max": int(sulp), "switch_sums_off_by_one": int(soff),
+                "switch_sums_checked": steps * N * sh,
+                "against": "CPU oracle fed with the sums the switch returned (left in the gradient "
+                           "buffer): everything bit for bit; the sums themselves against the "
+                           "rank-ordered fp32 sum with one fp16 rounding: within one fp16 ulp"})
+            out["ok"] = bool(all_flags and all_scale and worst == 0.0 and ulp == 0 and sulp <= 1)
+        else:
+            out["against"] = ("CPU oracle: rank-ordered fp32 sum, one fp16 rounding, reference "
+                              "update; tolerance 1e-6 per step (bit differences reported)")
+            out["ok"] = bool(all_flags and all_scale and worst <= 1e-6 * steps and ulp <= 1)
     finally:
         w = g = wf = gf = None
         env.barrier()
@@ -522,44 +576,33 @@ def config2_as_written(env, grp, n, steps):
 
 # ------------------------------------------------------- NVLink copy, this run
 
-def peer_copy_leg(env, mbytes=256):
-    """NVLink bandwidth per direction as this run sees it: a ring of NCCL send/recv
-    (every rank sends `mbytes` MB to the next rank and receives from the previous one, all
-    at once), and one pair alone (rank 0 to rank 1, nothing else on the fabric)."""
-    torch, dist = env.torch, env.dist
-    n = mbytes << 20
-    src = torch.empty(n, dtype=torch.uint8, device=env.dev)
-    dst = torch.empty(n, dtype=torch.uint8, device=env.dev)
-    nxt, prv = (env.rank + 1) % env.world, (env.rank - 1) % env.world
-
-    def ring():
-        ops = [dist.P2POp(dist.isend, src, nxt), dist.P2POp(dist.irecv, dst, prv)]
-        for r in dist.batch_isend_irecv(ops):
-            r.wait()
-
-    def pair():
-        if env.rank == 0:
-            dist.send(src, 1)
-        elif env.rank == 1:
-            dist.recv(dst, 0)
-
+def peer_copy_leg(env, grp, nbytes):
+    """NVLink copy rate per direction as this run sees it, between the arenas the step
+    kernel uses: device-to-device copies of the fp16 weight buffer (identical on all
+    ranks) with the copy engines -- rank 0 alone pulling from rank 1, and every rank
+    pulling from the next one at the same time."""
+    torch = env.torch
+    nxt = (env.rank + 1) % env.world
     res = {}
-    for name, fn in (("ring_all_ranks", ring), ("one_pair", pair)):
-        for _ in range(3):
-            fn()
+    for name, active in (("one_pair", env.rank == 0), ("ring_all_ranks", True)):
+        peer = 1 if name == "one_pair" else nxt
+        for _ in range(2):
+            if active:
+                grp.peer_copy(peer, nbytes, env.sp)
         env.barrier()
-        k = 10
+        k = 20
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(env.stream)
         for _ in range(k):
-            fn()
+            if active:
+                grp.peer_copy(peer, nbytes, env.sp)
         b.record(env.stream)
         torch.cuda.synchronize(env.dev)
         ms = env.max_over_ranks([a.elapsed_time(b) / k])[0]
         env.barrier()
-        res[name + "_gbs"] = n / (ms * 1e-3) / 1e9
-    res["what"] = f"NCCL send/recv of {mbytes} MB per rank, GB/s per direction per GPU, max over ranks"
-    del src, dst
+        res[name + "_gbs"] = nbytes / (ms * 1e-3) / 1e9
+    res["what"] = (f"cudaMemcpyAsync of {nbytes / 1e6:.0f} MB from a peer's arena, GB/s per "
+                   "direction per GPU, max over ranks")
     return res
 
 
@@ -573,7 +616,7 @@ def nccl_sequence_leg(env, grp, restore_path, k):
         grp.exec(LR, L2, SCALE0, env.sp)
     grp.flags(env.sp)
     env.barrier()
-    _, total = timed_steps(env, lambda: grp.exec(LR, L2, SCALE0, env.sp), k)
+    total = timed_block(env, lambda: grp.exec(LR, L2, SCALE0, env.sp), k)
     grp.flags(env.sp)
     env.barrier()
     set_path(grp, restore_path)
@@ -600,7 +643,7 @@ def allreduce_sequence_leg(env, n, w, g, k):
     for _ in range(3):
         ar_step()
     env.barrier()
-    _, total = timed_steps(env, ar_step, k)
+    total = timed_block(env, ar_step, k)
     env.barrier()
     del aw, ag, am, av, ac
     return env.max_over_ranks([total / k])[0]
@@ -642,7 +685,7 @@ def run_sweep(args):
                 grp.exec(LR, L2, SCALE0, env.sp)
             grp.flags(env.sp)
             env.barrier()
-            per, total = timed_steps(env, lambda: grp.exec(LR, L2, SCALE0, env.sp), k)
+            total = timed_block(env, lambda: grp.exec(LR, L2, SCALE0, env.sp), k)
             grp.flags(env.sp)
             env.barrier()
             us = env.max_over_ranks([total / k])[0] * 1e3
@@ -668,6 +711,64 @@ def run_sweep(args):
         env.dist.destroy_process_group()
 
 
+def run_tune(args):
+    """Tuning aid: several launch settings of the step kernel on the benchmark workload in
+    one process launch.  Not a benchmark value."""
+    env = Env(args)
+    torch = env.torch
+    from saga_b200 import FlatLayout, capi, workload
+    n = args.params or FlatLayout(workload.tensor_sizes(TOTAL_PARAMS, TENSORS)).total
+    grp, _, info = make_group(env, n, 0, "nvls" if env.world > 1 else "peer")
+    w, g = grp.buffers(capi.HALF)
+    gen = torch.Generator(device=env.dev).manual_seed(0x5A6A)
+    w.copy_((torch.randn(n, device=env.dev, generator=gen) * 0.02).half())
+    gen_g = torch.Generator(device=env.dev).manual_seed(0x5A6A + 1 + env.rank)
+    g.copy_((torch.randn(n, device=env.dev, generator=gen_g) * (1e-3 * SCALE0)).half())
+    grp.init_master(env.sp)
+    env.barrier()
+    rows = []
+    for spec in args.tune.split(","):
+        parts = spec.split(":")
+        path = parts[0]
+        share = int(parts[1]) if len(parts) > 1 and parts[1] else 0
+        ctas = int(parts[2]) if len(parts) > 2 and parts[2] else 0
+        variant = int(parts[3]) if len(parts) > 3 and parts[3] else 0
+        if path == "nvls" and not info["multicast"]:
+            continue
+        set_path(grp, path)
+        grp.set_option(capi.OPT_NVLS_PEER_SHARE, share)
+        grp.set_option(capi.OPT_CTAS_PER_SM, ctas)
+        grp.set_option(capi.OPT_KERNEL_VARIANT, variant)
+        fn = lambda: grp.exec(LR, L2, SCALE0, env.sp)   # noqa: E731
+        for _ in range(10):
+            fn()
+        grp.flags(env.sp)
+        env.barrier()
+        ms = env.max_over_ranks([timed_block(env, fn, args.steps)])[0]
+        grp.flags(env.sp)
+        env.barrier()
+        grp.set_option(capi.OPT_PHASE_TIMERS, 1)
+        ph = []
+        for _ in range(6):
+            for _ in range(20):
+                fn()
+            grp.flags(env.sp)
+            ph.append(grp.phase_times())
+            env.barrier()
+        grp.set_option(capi.OPT_PHASE_TIMERS, 0)
+        med = env.max_over_ranks(list(np.median(np.asarray(ph[1:], dtype=np.float64), axis=0) / 1e3))
+        rows.append({"setting": spec, "us_per_step": ms / args.steps * 1e3,
+                     "entry_wait_us": med[0], "body_end_us": med[1], "completion_us": med[2]})
+    if env.rank == 0:
+        print(json.dumps({"mode": "tune", "n_gpus": env.world, "n": n, "steps": args.steps,
+                          "rows": rows}), flush=True)
+    w = g = None
+    env.barrier()
+    grp.destroy()
+    if env.world > 1:
+        env.dist.destroy_process_group()
+
+
 # ------------------------------------------------------------------- our arm
 
 def main():
@@ -682,10 +783,12 @@ def main():
                     help="put the parameters in the fp32 group (the reference's AdamF32 path: "
                          "fp32 weights and gradients, no master copy) instead of the fp16 group")
     ap.add_argument("--e2e-steps", type=int, default=0, help="default: min(steps, 50)")
-    ap.add_argument("--config2-steps", type=int, default=800,
+    ap.add_argument("--config2-steps", type=int, default=2400,
                     help="steps of the config-2-as-written leg (N = 1; 0 switches it off)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--only-timed", action="store_true",
+                    help="tuning aid: the back-to-back timed loop and the phase timers only")
     ap.add_argument("--with-ref-gpu", action="store_true",
                     help="also time the reference's own compiled Adam kernel (oracle/_ref) as a "
                          "GPU baseline beside the CPU one; off by default")
@@ -693,6 +796,8 @@ def main():
     ap.add_argument("--variant", type=int, default=-1)
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--grid", type=int, default=0)
+    ap.add_argument("--peer-share", type=int, default=-1,
+                    help="multicast path: trips out of every 8 that take the peer-pointer arithmetic")
     ap.add_argument("--path", default="auto", choices=["auto", "peer", "nvls", "nccl"])
     ap.add_argument("--with-allreduce-baseline", action="store_true",
                     help="N > 1: also time NCCL all-reduce of the whole fp16 gradient buffer followed "
@@ -700,6 +805,9 @@ def main():
     ap.add_argument("--serial-ranks", type=int, default=0,
                     help="profiling aid: N ranks on ONE GPU, stepped one after the other "
                          "(no cross-GPU waits); times the N-rank kernel against local HBM only")
+    ap.add_argument("--tune", default="",
+                    help="tuning aid: comma-separated path[:peer_share[:ctas_per_sm]] settings, each "
+                         "timed for --steps steps on the benchmark workload; prints one JSON line")
     ap.add_argument("--sweep", action="store_true", help="config 5: sizes 2^20..2^30 at this N")
     ap.add_argument("--sweep-exps", default="20,22,24,26,28,30")
     args = ap.parse_args()
@@ -709,7 +817,12 @@ def main():
         return run_serial_ranks(args)
     if args.sweep:
         return run_sweep(args)
+    if args.tune:
+        return run_tune(args)
     args.warmup = max(args.warmup, 3)
+    if args.only_timed:
+        args.no_parity = args.no_cpu_baseline = True
+        args.config2_steps = 0
 
     env = Env(args)
     torch, dist = env.torch, env.dist
@@ -745,9 +858,11 @@ def main():
         wl = wl.replace("fp16", "fp32") + " (fp32 group)"
 
     # ---- parity of this run's collective path at this N, before anything is timed
-    parity = None
+    parity = parity_peer = None
     if not args.no_parity:
         parity = parity_leg(env, args.path)
+        if parity["path"] == "nvls":     # the bit-exact path at this N, for the record
+            parity_peer = parity_leg(env, "peer")
 
     grp, path, info = make_group(env, 0 if f32 else n, n if f32 else 0, args.path)
     live.append(grp)
@@ -759,6 +874,8 @@ def main():
         grp.set_option(capi.OPT_STAGES, args.stages)
     if args.grid:
         grp.set_option(capi.OPT_GRID, args.grid)
+    if args.peer_share >= 0 and path == "nvls":
+        grp.set_option(capi.OPT_NVLS_PEER_SHARE, args.peer_share)
 
     w, g = grp.buffers(capi.FLOAT if f32 else capi.HALF)
     gen = torch.Generator(device=dev).manual_seed(0x5A6A)          # same weights on every rank
@@ -783,47 +900,54 @@ def main():
     launches0 = grp.launch_count
     if sampler:
         sampler.start()
-    per_step, total_ms = timed_steps(env, step, args.steps)
+    total_ms = timed_block(env, step, args.steps)
     env.barrier()
     launches = grp.launch_count - launches0
     flags = grp.flags(sp)
     ms = env.max_over_ranks([total_ms])[0]
-    # per-step statistics of the slowest rank's view: element-wise max over ranks
+    # the distribution over steps comes from a second pass with an event between every two
+    # steps (the extra stream operations cost a few microseconds per step, so its mean sits
+    # above ms_per_step); element-wise max over ranks = the slowest rank's view
+    per_step, _ = timed_steps(env, step, min(args.steps, 300))
     per_step = env.max_over_ranks(per_step)
+    env.barrier()
 
-    # ---- where the kernel's time goes: its own timer stamps, read after every step
+    # ---- where the kernel's time goes: its own timer stamps.  The stamps of a launch are
+    # overwritten by the next one, so the last step of each back-to-back burst is read.
     phases = None
     if world > 1 and path != "nccl":
         grp.set_option(capi.OPT_PHASE_TIMERS, 1)
         rows = []
-        for i in range(60):
-            step()
+        for _ in range(12):
+            for _ in range(20):
+                step()
             grp.flags(sp)
-            if i >= 10:
-                rows.append(grp.phase_times())
-            if world > 1:
-                dist.barrier(device_ids=[env.local])
+            rows.append(grp.phase_times())
+            env.barrier()
         grp.set_option(capi.OPT_PHASE_TIMERS, 0)
-        med = np.median(np.asarray(rows, dtype=np.float64), axis=0) / 1e3
+        med = np.median(np.asarray(rows[2:], dtype=np.float64), axis=0) / 1e3
         med = env.max_over_ranks(list(med))
         phases = {"entry_wait_us": med[0], "entry_to_last_cta_done_us": med[1],
                   "completion_protocol_us": med[2], "kernel_total_us": med[3],
-                  "what": "median over 50 steps of the step kernel's own %globaltimer stamps, max "
-                          "over ranks; every step here is followed by a host read of the flags and "
-                          "a host barrier, so the ranks enter each step less tightly aligned than "
-                          "in the back-to-back timed loop"}
+                  "what": "the step kernel's own %globaltimer stamps: wait for the peers' "
+                          "announcements (first CTA; the first trip's local loads are already in "
+                          "flight), kernel entry until the last CTA finished its share, completion "
+                          "protocol in the last CTA, and their sum; 20th step of back-to-back "
+                          "bursts, median over 10 bursts, max over ranks"}
         env.barrier()
 
     # ---- N > 1: the reference's own sequence on the same buffers, for comparison
     nccl_ms = None
-    if world > 1 and path != "nccl":
+    if world > 1 and path != "nccl" and not args.only_timed:
         nccl_ms = nccl_sequence_leg(env, grp, path, min(args.steps, 200))
 
     allreduce_ms = None
     if world > 1 and args.with_allreduce_baseline and not f32:
         allreduce_ms = allreduce_sequence_leg(env, n, w, g, min(args.steps, 200))
 
-    peer_copy = peer_copy_leg(env) if world > 1 else None
+    peer_copy = None
+    if world > 1 and not args.only_timed and not f32 and path != "nccl":
+        peer_copy = peer_copy_leg(env, grp, n * 2)
 
     # ---- N = 1, on request: a second baseline beside cpu_baseline -- the reference's own
     # kernel (src/cuda/cuda_kernels.cu compiled unmodified for sm_100a, oracle/_ref) on
@@ -847,7 +971,7 @@ def main():
                 ref_step()
             torch.cuda.synchronize(dev)
             k = min(args.steps, 200)
-            _, rtotal = timed_steps(env, ref_step, k)
+            rtotal = timed_block(env, ref_step, k)
             rms = rtotal / k
             ref_gpu = {"kernel": "saga::adam_mixed, the reference's src/cuda/cuda_kernels.cu "
                                  "compiled unmodified for sm_100a",
@@ -858,7 +982,7 @@ def main():
     # ---- end to end through the C ABI: gradients start in pinned host memory,
     # every step copies them in, steps, waits, reads the flag sums back and
     # updates the loss scale on the host (what Saga's step tail does)
-    e2e_steps = args.e2e_steps or min(args.steps, 50)
+    e2e_steps = 3 if args.only_timed else (args.e2e_steps or min(args.steps, 50))
     for _ in range(3):
         grp.step_host(host_ptrs[0], host_ptrs[1], LR, L2, scaler.scale, sp)
     env.barrier()
@@ -911,7 +1035,9 @@ def main():
             "unit": "params/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": per_step_ms,
-            "step_us": summarize(per_step),
+            "step_us": dict(summarize(per_step),
+                            note="second pass with an event between every two steps, which "
+                                 "adds a few us per step; ms_per_step is the one-event-pair mean"),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": cfg,
@@ -942,8 +1068,8 @@ def main():
                 "bound": "nvlink", "achieved": nv, "peak": peak or NVLINK_NOMINAL_GBS,
                 "unit": "GB/s per direction per GPU",
                 "frac": nv / (peak or NVLINK_NOMINAL_GBS),
-                "peak_kind": "of measured (NCCL send/recv in this run, the larger of one pair and "
-                             "an all-rank ring)" if peak else "of nominal",
+                "peak_kind": "of measured (peer copies between the arenas in this run, the larger "
+                             "of one pair and an all-rank ring)" if peak else "of nominal",
                 "peak_nominal": NVLINK_NOMINAL_GBS, "frac_of_900_nominal": nv / NVLINK_NOMINAL_GBS,
                 "algorithmic_bytes_per_direction_per_launch": nv_alg,
                 "link_bytes_per_direction_of_this_path": link,
@@ -965,6 +1091,8 @@ def main():
                     "ms_per_step": nccl_ms, "speedup_of_fused_kernel": nccl_ms / per_step_ms}
         if parity is not None:
             line["parity"] = parity
+        if parity_peer is not None:
+            line["parity_peer_path"] = parity_peer
         if allreduce_ms:
             line["allreduce_sequence"] = {
                 "what": "NCCL all-reduce of the whole fp16 gradient buffer + one-GPU Adam kernel over "
@@ -985,8 +1113,9 @@ def main():
     grp.destroy()
     if world > 1:
         dist.destroy_process_group()
-    if parity is not None and not parity.get("ok", False):
-        raise SystemExit("parity leg failed: " + json.dumps(parity))
+    for blk in (parity, parity_peer):
+        if blk is not None and not blk.get("ok", False):
+            raise SystemExit("parity leg failed: " + json.dumps(blk))
 
 
 if __name__ == "__main__":

@@ -60,8 +60,10 @@ extern "C" {
                                order, bit for bit reproducible */
 #define B200OPT_PATH_NCCL 2 /* ncclReduceScatter + Adam kernel + ncclAllGather */
 #define B200OPT_PATH_NVLS 3 /* fused kernel over an NVSwitch multicast mapping: the switch
-                               sums the gradients (its own order, like NCCL's) and
-                               replicates the weights; needs B200OPT_CREATE_MULTICAST */
+                               sums the fp16 gradients (its own arithmetic: within one fp16
+                               ulp of the correctly rounded sum, the same NCCL's NVLS
+                               reduce-scatter has) and replicates the weights; needs
+                               B200OPT_CREATE_MULTICAST */
 
 /* options */
 #define B200OPT_OPT_TIMEOUT_MS 1    /* limit of every cross-GPU wait (default 10000) */
@@ -74,6 +76,14 @@ extern "C" {
 #define B200OPT_OPT_PHASE_TIMERS 8  /* 1: the step kernel records where its time went (b200opt_phase_times) */
 #define B200OPT_OPT_ASSUME_NO_PEER_ACCESS 9 /* test aid, set before wiring: treat every other GPU as
                                                unreachable, as on a machine without peer access */
+
+#define B200OPT_OPT_KEEP_REDUCED 10 /* multicast path: 1 leaves the switch-reduced gradients of the own
+                                       shard in the own gradient buffer (where ncclReduceScatter leaves
+                                       them in place in the reference), so that a caller can check the
+                                       update against the sum it was computed from */
+
+#define B200OPT_OPT_NVLS_PEER_SHARE 11 /* multicast path: k of every 8 trips of a CTA take the peer-pointer
+                                          arithmetic instead of the switch's (0..8, default 0) */
 
 /* creation flags for b200opt_create_ex / b200opt_create_group_ex */
 #define B200OPT_CREATE_FABRIC 1u    /* weight/gradient arena from CUDA's virtual-memory API: shared
@@ -438,6 +448,15 @@ B200OPT_API int b200opt_get_option(const b200opt_t *h, int option, long *value);
  *   [3] kernel entry until the end of the completion protocol
  */
 B200OPT_API int b200opt_phase_times(const b200opt_t *h, uint64_t ns_out[4]);
+
+/*
+ * Measurement aid: copies the first `bytes` of the peer rank's fp16 weight
+ * buffer over this rank's, on `stream`, with the GPU's copy engines.  After
+ * any completed step all ranks hold the same weights, so the copy changes
+ * nothing; it lets a benchmark measure the NVLink copy rate between the very
+ * arenas the step kernel uses.  No counterpart in the reference.
+ */
+B200OPT_API int b200opt_peer_copy(b200opt_t *h, int peer_rank, size_t bytes, void *stream);
 
 /* Kernel launches this handle has issued since creation (its own kernels and,
  * on the NCCL path, the NCCL calls). */

@@ -203,6 +203,28 @@ class MultiRankState:
         return tuple(int(x) for x in sums)
 
 
+def half_ulp_distance(a_bits, b_bits):
+    """Distance between fp16 bit patterns in units in the last place, element-wise (finite
+    values on a sign-magnitude number line; +0 and -0 coincide).  Where either value is inf
+    or NaN the distance is 0 if both have the same class and sign, else a large number."""
+    a = np.asarray(a_bits, dtype=np.uint16).astype(np.int64)
+    b = np.asarray(b_bits, dtype=np.uint16).astype(np.int64)
+
+    def line(x):
+        mag = x & 0x7FFF
+        return np.where(x & 0x8000, -mag, mag)
+    d = np.abs(line(a) - line(b))
+    special = ((a & 0x7C00) == 0x7C00) | ((b & 0x7C00) == 0x7C00)
+    same = ((a & 0xFC00) == (b & 0xFC00)) & (((a & 0x3FF) != 0) == ((b & 0x3FF) != 0))
+    return np.where(special, np.where(same, 0, 1 << 20), d)
+
+
+def rank_ordered_sum_half(grads):
+    """fp32 sum of the ranks' fp16 buffers in rank order, one rounding to fp16."""
+    out = np.empty(grads[0].size, np.uint16)
+    return reduce_half_threads([np.ascontiguousarray(g, dtype=np.uint16) for g in grads], out)
+
+
 # ------------------------------------------------- reference kernels (GPU only)
 
 def ref_available():

@@ -80,6 +80,8 @@ struct b200opt {
     long stages = 0;
     long grid = 0;
     long timing = 0;
+    long keep_reduced = 0;
+    long peer_share = 0;
     long assume_no_peer_access = 0;  // test aid: wire as if the GPUs had no peer access
     long nccl_crossover = 0;
     uint64_t launches = 0;
@@ -186,10 +188,13 @@ cudaError_t launch_direct(const StepParams &p, int grid, cudaStream_t st)
     return cudaGetLastError();
 }
 
-template <int NR, int UNR, int MINB>
+template <int NR>
 cudaError_t launch_nvls(const StepParams &p, int grid, cudaStream_t st)
 {
-    nvls_step_kernel<NR, UNR, MINB><<<grid, kThreads, 0, st>>>(p);
+    if(p.peer_share > 0)
+        nvls_step_kernel<NR, true, 2><<<grid, kThreads, 0, st>>>(p);
+    else
+        nvls_step_kernel<NR, false, 3><<<grid, kThreads, 0, st>>>(p);
     return cudaGetLastError();
 }
 
@@ -284,8 +289,9 @@ cudaError_t launch_step(const StepParams &p, int nranks, int num_sms,
         return cudaErrorInvalidValue;
     }
     const size_t groups = std::max(p.h.ngroups, p.f.ngroups);
-    // measured at 25.6 M parameters: 2 CTAs per SM up to four ranks, 3 beyond
-    const long def_ctas = t.nvls ? 3 : (nranks <= 4 ? 2 : 3);
+    // measured at 25.6 M parameters: 2 CTAs per SM up to four ranks, 3 beyond;
+    // the multicast kernel does best with 2
+    const long def_ctas = t.nvls ? 2 : (nranks <= 4 ? 2 : 3);
     const long cps = t.ctas_per_sm > 0 ? t.ctas_per_sm : def_ctas;
     size_t want = (groups + (size_t)kThreads - 1) / (size_t)kThreads;
     if(want == 0)
@@ -294,13 +300,13 @@ cudaError_t launch_step(const StepParams &p, int nranks, int num_sms,
         want, t.grid > 0 ? (size_t)t.grid : (size_t)num_sms * cps);
     if(t.nvls) {
         switch(nranks) {
-        case 2: return launch_nvls<2, 1, 3>(p, grid, st);
-        case 3: return launch_nvls<3, 1, 3>(p, grid, st);
-        case 4: return launch_nvls<4, 1, 3>(p, grid, st);
-        case 5: return launch_nvls<5, 1, 3>(p, grid, st);
-        case 6: return launch_nvls<6, 1, 3>(p, grid, st);
-        case 7: return launch_nvls<7, 1, 3>(p, grid, st);
-        case 8: return launch_nvls<8, 1, 3>(p, grid, st);
+        case 2: return launch_nvls<2>(p, grid, st);
+        case 3: return launch_nvls<3>(p, grid, st);
+        case 4: return launch_nvls<4>(p, grid, st);
+        case 5: return launch_nvls<5>(p, grid, st);
+        case 6: return launch_nvls<6>(p, grid, st);
+        case 7: return launch_nvls<7>(p, grid, st);
+        case 8: return launch_nvls<8>(p, grid, st);
         }
         return cudaErrorInvalidValue;
     }
@@ -992,6 +998,8 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
     p.partial = last ? 0 : 1;
     p.barrier = (h->nranks > 1 && !h->serial) ? 1 : 0;
     if(tune.nvls) {
+        p.keep_reduced = h->keep_reduced ? 1 : 0;
+        p.peer_share = (int)h->peer_share;
         p.mcG = reinterpret_cast<const uint16_t *>(h->mc.va + h->off_gh);
         p.mcW = reinterpret_cast<uint16_t *>(h->mc.va + h->off_wh);
     }
@@ -1489,6 +1497,14 @@ int b200opt_set_option(b200opt_t *h, int option, long value)
     case B200OPT_OPT_PHASE_TIMERS:
         h->timing = value != 0;
         return B200OPT_OK;
+    case B200OPT_OPT_KEEP_REDUCED:
+        h->keep_reduced = value != 0;
+        return B200OPT_OK;
+    case B200OPT_OPT_NVLS_PEER_SHARE:
+        if(value < 0 || value > 8)
+            return B200OPT_EINVAL;
+        h->peer_share = value;
+        return B200OPT_OK;
     case B200OPT_OPT_ASSUME_NO_PEER_ACCESS:
         if(h->peers_attached > 1)
             return fail(h, B200OPT_ESTATE, "set before any peer is attached");
@@ -1511,11 +1527,27 @@ int b200opt_get_option(const b200opt_t *h, int option, long *value)
     case B200OPT_OPT_STAGES: *value = h->stages; return B200OPT_OK;
     case B200OPT_OPT_GRID: *value = h->grid; return B200OPT_OK;
     case B200OPT_OPT_PHASE_TIMERS: *value = h->timing; return B200OPT_OK;
+    case B200OPT_OPT_KEEP_REDUCED: *value = h->keep_reduced; return B200OPT_OK;
+    case B200OPT_OPT_NVLS_PEER_SHARE: *value = h->peer_share; return B200OPT_OK;
     case B200OPT_OPT_ASSUME_NO_PEER_ACCESS:
         *value = h->assume_no_peer_access;
         return B200OPT_OK;
     }
     return B200OPT_EINVAL;
+}
+
+int b200opt_peer_copy(b200opt_t *h, int peer_rank, size_t bytes, void *stream)
+{
+    if(!h || peer_rank < 0 || peer_rank >= h->nranks || peer_rank == h->rank)
+        return B200OPT_EINVAL;
+    if(!h->peer_arena[peer_rank] || h->serial)
+        return fail(h, B200OPT_ESTATE, "the peer's memory is not mapped from another GPU");
+    if(bytes > h->n_half * 2)
+        return fail(h, B200OPT_EINVAL, "more bytes than the fp16 weight buffer holds");
+    DeviceGuard guard(h->device);
+    CK(h, cudaMemcpyAsync(h->arena + h->off_wh, h->peer_arena[peer_rank] + h->off_wh,
+                          bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    return B200OPT_OK;
 }
 
 int b200opt_phase_times(const b200opt_t *h, uint64_t ns_out[4])

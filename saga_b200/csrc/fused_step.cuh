@@ -124,10 +124,15 @@ struct StepParams {
     uint32_t *scale_log;    // ring of {range, inf, nan, bits of the new scale} per step
     uint32_t scale_log_cap; // entries in the ring (0: no log)
     int timing;             // 1: record the phase timers
+    int keep_reduced;       // 1 (multicast path): leave the reduced gradients of the own
+                            // shard in the own gradient buffer, where ncclReduceScatter
+                            // leaves them in Saga (src/cuda/cuda_optimizer.cpp:160-166)
     // multicast views of the fp16 gradient and weight buffers of all ranks
     // (switch-reduced loads, switch-replicated stores); null off that path
     const uint16_t *mcG;
     uint16_t *mcW;
+    int peer_share;         // multicast path: trips out of every 8 that take the
+                            // peer-pointer arithmetic instead (0..8)
 };
 
 // 1/scale of this step: from the launch arguments, or from the scale that
@@ -337,11 +342,25 @@ struct HalfLoads {
     uint4 m0, m1, v0, v1, c0, c1;
 };
 
+// The local half of a group's loads: m, v and the master copy of the shard.
 template <int NR>
-__device__ __forceinline__ void half_load(const StepParams &p, size_t idx0,
-                                          HalfLoads<NR> &L)
+__device__ __forceinline__ void half_load_state(const StepParams &p, size_t idx0,
+                                                HalfLoads<NR> &L)
 {
     const size_t li = idx0 - p.h.A;
+    L.m0 = ld_stream(p.h.m + li);
+    L.m1 = ld_stream(p.h.m + li + 4);
+    L.v0 = ld_stream(p.h.v + li);
+    L.v1 = ld_stream(p.h.v + li + 4);
+    L.c0 = ld_stream(p.h.c + li);
+    L.c1 = ld_stream(p.h.c + li + 4);
+}
+
+// The other half: the gradients of every rank (peers' through NVLink).
+template <int NR>
+__device__ __forceinline__ void half_load_grads(const StepParams &p, size_t idx0,
+                                                HalfLoads<NR> &L)
+{
 #pragma unroll
     for(int q = 0; q < NR; q++) {
         if(NR == 1)
@@ -349,12 +368,6 @@ __device__ __forceinline__ void half_load(const StepParams &p, size_t idx0,
         else
             L.g[q] = ld_peer(p.h.G[q] + idx0);
     }
-    L.m0 = ld_stream(p.h.m + li);
-    L.m1 = ld_stream(p.h.m + li + 4);
-    L.v0 = ld_stream(p.h.v + li);
-    L.v1 = ld_stream(p.h.v + li + 4);
-    L.c0 = ld_stream(p.h.c + li);
-    L.c1 = ld_stream(p.h.c + li + 4);
 }
 
 __device__ __forceinline__ void unpack8(const uint4 &a, const uint4 &b,
@@ -470,6 +483,8 @@ __device__ __noinline__ uint32_t half_scalar(const StepParams &p, float alpha,
                     *reinterpret_cast<const volatile uint16_t *>(p.h.G[q] + i));
             u = float_to_half_bits(acc);
         }
+        if(p.keep_reduced)
+            const_cast<uint16_t *>(p.h.G[p.rank])[i] = (uint16_t)u;
         if(classify_half(u, fl))
             continue;
         const size_t li = i - p.h.A;
@@ -594,28 +609,33 @@ __device__ __noinline__ uint32_t float_scalar(const StepParams &p, size_t idx0)
 
 // ------------------------------------------------- step prologue and epilogue
 
-// (N > 1) Announces "my gradients are final" to every rank and waits, bounded,
-// for every rank's announcement of the same step.  Returns non-zero in every
-// thread of the CTA when a wait ran out.
+// (N > 1) Announces "my gradients are final" to every rank.  The step kernels
+// call this first, start the loads of their own shard state, and only then
+// wait for the peers (step_wait): the state is local and final, only the
+// peers' gradients depend on the announcements.
 template <int NR>
-__device__ __forceinline__ int step_begin(const StepParams &p)
+__device__ __forceinline__ void step_announce(const StepParams &p)
 {
-    if(NR == 1 || !p.barrier) {
-        if(p.timing && blockIdx.x == 0 && threadIdx.x == 0 && p.ctrl[p.rank]) {
-            p.ctrl[p.rank]->t_start = globaltimer_ns();
-            p.ctrl[p.rank]->t_entry_wait = 0;
-        }
-        return 0;
+    Ctrl *const my = p.ctrl[p.rank];
+    if(p.timing && blockIdx.x == 0 && threadIdx.x == 0 && my) {
+        my->t_start = globaltimer_ns();
+        my->t_entry_wait = 0;
     }
+    if(NR == 1 || !p.barrier)
+        return;
+    if(blockIdx.x == 0 && threadIdx.x < NR)
+        st_release_sys(&p.ctrl[threadIdx.x]->ready[p.rank], p.epoch);
+}
+
+// Waits, bounded, for every rank's announcement of this step.  Returns
+// non-zero in every thread of the CTA when a wait ran out.
+template <int NR>
+__device__ __forceinline__ int step_wait(const StepParams &p)
+{
+    if(NR == 1 || !p.barrier)
+        return 0;
     const int tid = threadIdx.x;
     Ctrl *const my = p.ctrl[p.rank];
-    unsigned long long t0 = 0;
-    if(p.timing && blockIdx.x == 0 && tid == 0) {
-        t0 = globaltimer_ns();
-        my->t_start = t0;
-    }
-    if(blockIdx.x == 0 && tid < NR)
-        st_release_sys(&p.ctrl[tid]->ready[p.rank], p.epoch);
     int bad = 0;
     if(tid < NR) {
         if(!wait_epoch(&my->ready[tid], p.epoch, p.timeout_ns)) {
@@ -629,8 +649,16 @@ __device__ __forceinline__ int step_begin(const StepParams &p)
     }
     bad = __syncthreads_or(bad);
     if(p.timing && blockIdx.x == 0 && tid == 0)
-        my->t_entry_wait = globaltimer_ns() - t0;
+        my->t_entry_wait = globaltimer_ns() -
+                           *reinterpret_cast<volatile unsigned long long *>(&my->t_start);
     return bad;
+}
+
+template <int NR>
+__device__ __forceinline__ int step_begin(const StepParams &p)
+{
+    step_announce<NR>(p);
+    return step_wait<NR>(p);
 }
 
 // The fp32 group (BatchNorm scales and biases in an fp16 network: a few tens
@@ -787,7 +815,8 @@ __device__ __forceinline__ void step_finish(const StepParams &p, uint32_t fl,
 // ------------------------------------------------ step kernel, direct loads
 
 // Every thread loads its 8-element groups straight into registers (UNR groups
-// before any is computed, to keep enough bytes in flight per SM).
+// before any is computed, to keep enough bytes in flight per SM).  The loads
+// of the first trip's shard state are issued before the wait for the peers.
 template <int NR, int UNR, int MINB>
 __global__ void __launch_bounds__(kThreads, MINB)
     fused_step_kernel(const __grid_constant__ StepParams p)
@@ -795,24 +824,48 @@ __global__ void __launch_bounds__(kThreads, MINB)
     __shared__ int s_flag;
     const int tid = threadIdx.x;
     uint32_t fl = 0;
-    if(!step_begin<NR>(p)) {
-        const float alpha = step_alpha(p);
-        const size_t stride = (size_t)gridDim.x * kThreads * UNR;
-        const size_t ng = p.h.ngroups;
-        const size_t lo = p.h.o, hi = p.h.o + p.h.s;
-        for(size_t base = (size_t)blockIdx.x * kThreads * UNR; base < ng;
-            base += stride) {
-            HalfLoads<NR> L[UNR];
-            bool full[UNR];
+    const size_t stride = (size_t)gridDim.x * kThreads * UNR;
+    const size_t ng = p.h.ngroups;
+    const size_t lo = p.h.o, hi = p.h.o + p.h.s;
+    size_t base = (size_t)blockIdx.x * kThreads * UNR;
+    HalfLoads<NR> L[UNR];
+    bool full[UNR];
+
+    auto classify = [&](size_t b) {
 #pragma unroll
-            for(int k = 0; k < UNR; k++) {
-                const size_t gid = base + (size_t)k * kThreads + tid;
-                const size_t idx0 = p.h.B + gid * kVec;
-                full[k] = gid < ng && idx0 >= lo && idx0 + kVec <= hi &&
-                          !p.force_scalar;
-                if(full[k])
-                    half_load<NR>(p, idx0, L[k]);
+        for(int k = 0; k < UNR; k++) {
+            const size_t gid = b + (size_t)k * kThreads + tid;
+            const size_t idx0 = p.h.B + gid * kVec;
+            full[k] = gid < ng && idx0 >= lo && idx0 + kVec <= hi && !p.force_scalar;
+        }
+    };
+    auto load_state = [&](size_t b) {
+#pragma unroll
+        for(int k = 0; k < UNR; k++)
+            if(full[k])
+                half_load_state<NR>(p, p.h.B + (b + (size_t)k * kThreads + tid) * kVec, L[k]);
+    };
+
+    step_announce<NR>(p);
+    bool state_loaded = false;
+    if(base < ng) {
+        classify(base);
+        load_state(base);
+        state_loaded = true;
+    }
+    if(!step_wait<NR>(p)) {
+        const float alpha = step_alpha(p);
+        for(; base < ng; base += stride) {
+            if(!state_loaded) {
+                classify(base);
+                load_state(base);
             }
+            state_loaded = false;
+#pragma unroll
+            for(int k = 0; k < UNR; k++)
+                if(full[k])
+                    half_load_grads<NR>(p, p.h.B + (base + (size_t)k * kThreads + tid) * kVec,
+                                        L[k]);
 #pragma unroll
             for(int k = 0; k < UNR; k++) {
                 const size_t gid = base + (size_t)k * kThreads + tid;

@@ -1,18 +1,23 @@
 // Step kernel over an NVSwitch multicast mapping (sm_100a, N > 1 GPUs): the
 // gradients of the rank's shard are fetched with ONE switch-reduced load per
 // 16 bytes (multimem.ld_reduce: the switch reads the same address in every
-// rank's gradient buffer, adds in fp32 and returns the fp16-rounded sum) and
+// rank's gradient buffer, adds the values and returns the fp16 sum) and
 // the updated fp16 weights leave the GPU ONCE (multimem.st: the switch writes
 // them into every rank's weight buffer).  Per rank and NVLink direction that
 // is about 2n + 2n/N bytes for n fp16 parameters instead of the 4n(N-1)/N of
 // the peer-pointer kernel, which loads every peer's copy and stores to every
 // peer separately.
 //
-// The order in which the switch adds the N values is the hardware's, as
-// NCCL's is in Saga (ncclReduceScatter, src/cuda/cuda_optimizer.cpp:160-166
-// of the Saga tree); the peer-pointer kernel, which adds in rank order, stays
-// the path that is bit for bit equal to the rank-ordered oracle.  Everything
-// after the sum (classification, unscale, Adam, rounding) is the same code.
+// The sum is the switch's: measured on B200 / NVSwitch, multimem.ld_reduce on
+// f16x2 is deterministic but lands one fp16 ulp beside the correctly rounded
+// sum for about a fifth of the elements (with or without .acc::f32; the f32
+// form of the instruction is exact).  That is the arithmetic NCCL's own NVLS
+// reduce-scatter has on this machine, i.e. what Saga gets from
+// ncclReduceScatter (src/cuda/cuda_optimizer.cpp:160-166 of the Saga tree);
+// the peer-pointer kernel, which adds in fp32 in rank order and rounds once,
+// stays the path that is bit for bit equal to the rank-ordered oracle.
+// Everything after the sum (classification, unscale, Adam, rounding) is the
+// same code on both paths and bit-exact given the sum.
 //
 // The fp32 group (a few tens of thousands of BatchNorm parameters) and the
 // ragged 8-element groups at the shard's ends go through the peer pointers.
@@ -22,7 +27,7 @@
 
 namespace b200 {
 
-// 8 fp16 values summed over all ranks by the switch, fp32 accumulation.
+// 8 fp16 values summed over all ranks by the switch.
 __device__ __forceinline__ uint4 multimem_ld_reduce_f16x8(const void *mc)
 {
     uint4 v;
@@ -44,46 +49,105 @@ __device__ __forceinline__ void multimem_st_16(void *mc, const uint4 &v)
                  : "memory");
 }
 
-template <int NR, int UNR, int MINB>
+// PEER_MIX: the kernel also carries the peer-pointer arithmetic and runs it on
+// p.peer_share of every 8 trips of a CTA (0 = multicast only).  The switch's
+// reduce and replicate engines and plain peer traffic are separate limits of
+// the fabric; splitting the shard between them moves the step below either
+// one alone.
+template <int NR, bool PEER_MIX, int MINB>
 __global__ void __launch_bounds__(kThreads, MINB)
     nvls_step_kernel(const __grid_constant__ StepParams p)
 {
     __shared__ int s_flag;
     const int tid = threadIdx.x;
     uint32_t fl = 0;
-    if(!step_begin<NR>(p)) {
+    const size_t stride = (size_t)gridDim.x * kThreads;
+    const size_t ng = p.h.ngroups;
+    const size_t lo = p.h.o, hi = p.h.o + p.h.s;
+    size_t base = (size_t)blockIdx.x * kThreads;
+    HalfLoads<PEER_MIX ? NR : 1> L;
+    bool full = false;
+    size_t idx0 = 0;
+
+    auto classify = [&](size_t b) {
+        const size_t gid = b + tid;
+        idx0 = p.h.B + gid * kVec;
+        full = gid < ng && idx0 >= lo && idx0 + kVec <= hi;
+    };
+
+    step_announce<NR>(p);
+    bool state_loaded = false;
+    if(base < ng) {
+        classify(base);
+        if(full)
+            half_load_state(p, idx0, L);
+        state_loaded = true;
+    }
+    if(!step_wait<NR>(p)) {
         const float alpha = step_alpha(p);
-        const size_t stride = (size_t)gridDim.x * kThreads * UNR;
-        const size_t ng = p.h.ngroups;
-        const size_t lo = p.h.o, hi = p.h.o + p.h.s;
-        for(size_t base = (size_t)blockIdx.x * kThreads * UNR; base < ng;
-            base += stride) {
-            HalfLoads<1> L[UNR];
-            bool full[UNR];
-#pragma unroll
-            for(int k = 0; k < UNR; k++) {
-                const size_t gid = base + (size_t)k * kThreads + tid;
-                const size_t idx0 = p.h.B + gid * kVec;
-                full[k] = gid < ng && idx0 >= lo && idx0 + kVec <= hi;
-                if(full[k]) {
-                    const size_t li = idx0 - p.h.A;
-                    L[k].g[0] = multimem_ld_reduce_f16x8(p.mcG + idx0);
-                    L[k].m0 = ld_stream(p.h.m + li);
-                    L[k].m1 = ld_stream(p.h.m + li + 4);
-                    L[k].v0 = ld_stream(p.h.v + li);
-                    L[k].v1 = ld_stream(p.h.v + li + 4);
-                    L[k].c0 = ld_stream(p.h.c + li);
-                    L[k].c1 = ld_stream(p.h.c + li + 4);
-                }
+        for(size_t trip = 0; base < ng; base += stride, trip++) {
+            if(!state_loaded) {
+                classify(base);
+                if(full)
+                    half_load_state(p, idx0, L);
             }
+            state_loaded = false;
+            // the same choice in every thread of the CTA and on every rank
+            const bool via_peers =
+                PEER_MIX && (int)((blockIdx.x + trip) & 7u) < p.peer_share;
+            if(full) {
+                if(via_peers) {
+                    if(PEER_MIX) {
+                        half_load_grads<PEER_MIX ? NR : 1>(p, idx0, L);
+                        uint4 out[7];
+                        half_compute<PEER_MIX ? NR : 1>(p, alpha, idx0, L, fl, out);
+                        const size_t li = idx0 - p.h.A;
+                        st_stream(p.h.m + li, out[0]);
+                        st_stream(p.h.m + li + 4, out[1]);
+                        st_stream(p.h.v + li, out[2]);
+                        st_stream(p.h.v + li + 4, out[3]);
+                        st_stream(p.h.c + li, out[4]);
+                        st_stream(p.h.c + li + 4, out[5]);
 #pragma unroll
-            for(int k = 0; k < UNR; k++) {
-                const size_t gid = base + (size_t)k * kThreads + tid;
-                const size_t idx0 = p.h.B + gid * kVec;
-                if(full[k]) {
+                        for(int q = 0; q < NR; q++)
+                            *reinterpret_cast<uint4 *>(p.h.W[q] + idx0) = out[6];
+                        if(p.keep_reduced) {
+                            // the rank-ordered sum this arm formed, recomputed for the record
+                            uint32_t u[8];
+                            float acc[8];
+                            halves8(L.g[0], u);
+#pragma unroll
+                            for(int e = 0; e < 8; e++)
+                                acc[e] = half_bits_to_float(u[e]);
+#pragma unroll
+                            for(int q = 1; q < (PEER_MIX ? NR : 1); q++) {
+                                uint32_t t8[8];
+                                halves8(L.g[q], t8);
+#pragma unroll
+                                for(int e = 0; e < 8; e++)
+                                    acc[e] += half_bits_to_float(t8[e]);
+                            }
+#pragma unroll
+                            for(int e = 0; e < 8; e++)
+                                u[e] = float_to_half_bits(acc[e]);
+                            *reinterpret_cast<uint4 *>(
+                                const_cast<uint16_t *>(p.h.G[p.rank]) + idx0) =
+                                make_uint4(u[0] | (u[1] << 16), u[2] | (u[3] << 16),
+                                           u[4] | (u[5] << 16), u[6] | (u[7] << 16));
+                        }
+                    }
+                } else {
+                    HalfLoads<1> S;
+                    S.g[0] = multimem_ld_reduce_f16x8(p.mcG + idx0);
+                    S.m0 = L.m0;
+                    S.m1 = L.m1;
+                    S.v0 = L.v0;
+                    S.v1 = L.v1;
+                    S.c0 = L.c0;
+                    S.c1 = L.c1;
                     uint4 out[7];
                     // the sum is already formed: the one-rank arithmetic
-                    half_compute<1>(p, alpha, idx0, L[k], fl, out);
+                    half_compute<1>(p, alpha, idx0, S, fl, out);
                     const size_t li = idx0 - p.h.A;
                     st_stream(p.h.m + li, out[0]);
                     st_stream(p.h.m + li + 4, out[1]);
@@ -92,9 +156,12 @@ __global__ void __launch_bounds__(kThreads, MINB)
                     st_stream(p.h.c + li, out[4]);
                     st_stream(p.h.c + li + 4, out[5]);
                     multimem_st_16(p.mcW + idx0, out[6]);
-                } else if(gid < ng && idx0 + kVec > lo) {
-                    fl |= half_scalar<NR>(p, alpha, idx0);
+                    if(p.keep_reduced)
+                        *reinterpret_cast<uint4 *>(
+                            const_cast<uint16_t *>(p.h.G[p.rank]) + idx0) = S.g[0];
                 }
+            } else if(base + tid < ng && idx0 + kVec > lo) {
+                fl |= half_scalar<NR>(p, alpha, idx0);
             }
         }
         float_group_pass<NR>(p, fl);

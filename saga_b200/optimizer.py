@@ -283,6 +283,10 @@ class AdamGroup:
         check(lib().b200opt_get_option(self._h, option, C.byref(v)), self._h)
         return v.value
 
+    def peer_copy(self, peer_rank, nbytes, stream=0):
+        """Measurement aid: the peer's fp16 weights copied over this rank's (same values)."""
+        check(lib().b200opt_peer_copy(self._h, peer_rank, nbytes, C.c_void_p(stream)), self._h)
+
     def phase_times(self):
         """(entry wait, entry..last CTA done, completion protocol, total) of the last step
         kernel in ns; needs OPT_PHASE_TIMERS and a preceding flags()."""

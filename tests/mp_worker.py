@@ -113,6 +113,8 @@ def run_gpu(out_path, path="peer"):
         dist.destroy_process_group()
         return
     grp.set_option(capi.OPT_PATH, {"nccl": capi.PATH_NCCL, "nvls": capi.PATH_NVLS}.get(path, capi.PATH_PEER))
+    if path == "nvls":
+        grp.set_option(capi.OPT_KEEP_REDUCED, 1)
     sp = torch.cuda.current_stream(dev).cuda_stream
     W0, Wf0 = synth.weights_half(n_half, seed=9), synth.weights_float(n_float, seed=9)
     w, g = grp.buffers(capi.HALF)
@@ -133,6 +135,18 @@ def run_gpu(out_path, path="peer"):
         gf.copy_(torch.from_numpy(Gf[rank].copy()))
         grp.exec(1e-2, 0.01, scaler.scale, sp)
         flags = grp.flags(sp)
+        if path == "nvls":
+            # the oracle is fed with the switch's sums, which every rank left in its own
+            # shard of the gradient buffer: within one fp16 ulp of the rank-ordered sum
+            sh = n_half // world
+            parts = [None] * world
+            dist.all_gather_object(parts, g[rank * sh:(rank + 1) * sh].view(torch.int16).cpu()
+                                   .numpy().view(np.uint16).tobytes())
+            reduced = G[0].copy()
+            reduced[:world * sh] = np.frombuffer(b"".join(parts), dtype=np.uint16)
+            d = orc.half_ulp_distance(reduced, orc.rank_ordered_sum_half(G))
+            assert int(d[:world * sh].max()) <= 1, (rank, step, int(d.max()))
+            G = [reduced] + [np.full(n_half, 0x8000, np.uint16) for _ in range(world - 1)]
         oflags = ost.step([x.copy() for x in G], [x.copy() for x in Gf], scaler.scale, 1e-2, 0.01)
         if path != "nccl":
             assert flags == oflags, (rank, step, flags, oflags)
