@@ -434,6 +434,39 @@ B200OPT_API int b200opt_export_state(b200opt_t *h, int dtype, int which, float *
 B200OPT_API int b200opt_import_state(b200opt_t *h, int dtype, int which,
                          const float *host_src, size_t count);
 
+/* This handle's rank and the number of ranks it was created for. */
+B200OPT_API int b200opt_rank_info(const b200opt_t *h, int *rank, int *nranks);
+
+/*
+ * One tensor in Saga's own file format (Tensor::save / Tensor::load,
+ * src/tensor.cpp:1382-1552): 8 bytes "sagaT001", u32 element type (0 float,
+ * 1 half), u32 rank (<= 8), rank x u32 dimensions, the elements in row-major
+ * order; written to "<path>.tmp" and renamed into place.  dtype is
+ * B200OPT_HALF or B200OPT_FLOAT.  b200opt_tensor_load fills whichever outputs
+ * are non-NULL; with data == NULL it only reads the header and reports the
+ * payload size through *bytes.  Host-only.
+ */
+B200OPT_API int b200opt_tensor_save(const char *path, int dtype, unsigned rank,
+                        const uint32_t *dims, const void *data);
+B200OPT_API int b200opt_tensor_load(const char *path, int *dtype, unsigned *rank,
+                        uint32_t dims[8], void *data, size_t capacity_bytes,
+                        size_t *bytes);
+
+/*
+ * Optimizer-state checkpoint of this rank in directory `dir` (which must
+ * exist), as Saga tensor files: adam.r<rank>of<nranks>.{half.m, half.v,
+ * half.master, float.m, float.v, meta}.saga.  The shard arrays are fp32
+ * vectors; "meta" holds the iteration counter, the loss scale passed in and
+ * the policy's clean-step count.  Saga's own Graph save keeps the weights
+ * (src/graph.cpp:60-104) and nothing else; with these files a resumed run
+ * continues bit for bit.  Loading refuses files written for another rank,
+ * rank count or buffer size.  Synchronous; call between steps.
+ */
+B200OPT_API int b200opt_checkpoint_save(b200opt_t *h, const char *dir, float scale,
+                            int policy_state);
+B200OPT_API int b200opt_checkpoint_load(b200opt_t *h, const char *dir, float *scale,
+                            int *policy_state);
+
 B200OPT_API int b200opt_set_option(b200opt_t *h, int option, long value);
 B200OPT_API int b200opt_get_option(const b200opt_t *h, int option, long *value);
 

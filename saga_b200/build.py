@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200opt.so")
 
-SOURCES = ["b200opt.cu", "host_logic.cpp", "nccl_path.cpp", "fabric.cpp"]
+SOURCES = ["b200opt.cu", "host_logic.cpp", "nccl_path.cpp", "fabric.cpp", "checkpoint.cpp"]
 HEADERS = ["fused_step.cuh", "staged_step.cuh", "nvls_step.cuh", "nccl_path.h", "fabric.h",
            os.path.join("..", "..", "include", "b200opt.h")]
 

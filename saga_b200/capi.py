@@ -70,6 +70,12 @@ SIGNATURES = {
     "b200opt_set_iter": (_i, [_vp, _i]),
     "b200opt_export_state": (_i, [_vp, _i, _i, _vp, _sz, C.POINTER(_sz)]),
     "b200opt_import_state": (_i, [_vp, _i, _i, _vp, _sz]),
+    "b200opt_rank_info": (_i, [_vp, C.POINTER(_i), C.POINTER(_i)]),
+    "b200opt_tensor_save": (_i, [C.c_char_p, _i, C.c_uint, _u32p, _vp]),
+    "b200opt_tensor_load": (_i, [C.c_char_p, C.POINTER(_i), C.POINTER(C.c_uint), _u32p, _vp, _sz,
+                                C.POINTER(_sz)]),
+    "b200opt_checkpoint_save": (_i, [_vp, C.c_char_p, _f, _i]),
+    "b200opt_checkpoint_load": (_i, [_vp, C.c_char_p, _fp, C.POINTER(_i)]),
     "b200opt_set_option": (_i, [_vp, _i, C.c_long]),
     "b200opt_get_option": (_i, [_vp, _i, C.POINTER(C.c_long)]),
     "b200opt_peer_copy": (_i, [_vp, _i, _sz, _vp]),

@@ -1373,6 +1373,17 @@ int b200opt_adam_mixed_static(size_t n, float alpha, void *weights,
                : B200OPT_ECUDA;
 }
 
+int b200opt_rank_info(const b200opt_t *h, int *rank, int *nranks)
+{
+    if(!h)
+        return B200OPT_EINVAL;
+    if(rank)
+        *rank = h->rank;
+    if(nranks)
+        *nranks = h->nranks;
+    return B200OPT_OK;
+}
+
 int b200opt_get_iter(const b200opt_t *h, int *iter)
 {
     if(!h || !iter)

@@ -275,6 +275,18 @@ class AdamGroup:
         check(lib().b200opt_import_state(self._h, dtype, which, a.ctypes.data_as(C.c_void_p),
                                          a.size), self._h)
 
+    def checkpoint_save(self, directory, scale, policy_state=0):
+        """m, v, master, iteration counter and loss scale as Saga tensor files in `directory`."""
+        check(lib().b200opt_checkpoint_save(self._h, str(directory).encode(), float(scale),
+                                            int(policy_state)), self._h)
+
+    def checkpoint_load(self, directory):
+        """Restores what checkpoint_save wrote; returns (scale, policy_state)."""
+        s, st = C.c_float(), C.c_int()
+        check(lib().b200opt_checkpoint_load(self._h, str(directory).encode(), C.byref(s),
+                                            C.byref(st)), self._h)
+        return np.float32(s.value), st.value
+
     def set_option(self, option, value):
         check(lib().b200opt_set_option(self._h, option, int(value)), self._h)
 
@@ -314,6 +326,28 @@ class TrainingStepTail:
         flags = self.group.flags(stream)
         self.scaler.update(flags)
         return flags
+
+
+def tensor_save(path, array):
+    """A numpy float16/float32 array as a Saga tensor file (Tensor::save's format)."""
+    a = np.ascontiguousarray(array)
+    dt = {np.dtype(np.float16): capi.HALF, np.dtype(np.float32): capi.FLOAT}[a.dtype]
+    dims = (C.c_uint32 * max(a.ndim, 1))(*a.shape)
+    check(lib().b200opt_tensor_save(str(path).encode(), dt, a.ndim, dims,
+                                    a.ctypes.data_as(C.c_void_p)))
+
+
+def tensor_load(path):
+    """The array stored in a Saga tensor file."""
+    dt, rank, nbytes = C.c_int(), C.c_uint(), C.c_size_t()
+    dims = (C.c_uint32 * 8)()
+    check(lib().b200opt_tensor_load(str(path).encode(), C.byref(dt), C.byref(rank), dims, None, 0,
+                                    C.byref(nbytes)))
+    out = np.empty(tuple(dims[i] for i in range(rank.value)),
+                   dtype=np.float16 if dt.value == capi.HALF else np.float32)
+    check(lib().b200opt_tensor_load(str(path).encode(), None, None, None,
+                                    out.ctypes.data_as(C.c_void_p), out.nbytes, None))
+    return out
 
 
 def adam_mixed(n, alpha, weights_ptr, grads_ptr, m_ptr, v_ptr, c_ptr, b1t, b2t, lr, l2,

@@ -335,6 +335,72 @@ def test_export_import_state_resumes_exactly(oracle):
         assert np.array_equal(straight[key], resumed[key])
 
 
+def test_checkpoint_files_resume_exactly(oracle, tmp_path):
+    """m, v, master, iteration counter and loss scale through Saga tensor files: a run
+    resumed from the files continues bit for bit; files of another layout are refused."""
+    from saga_b200 import optimizer as optmod
+    n_half, n_float = 4112, 528
+    W0, Wf0 = synth.weights_half(n_half, seed=12), synth.weights_float(n_float, seed=12)
+
+    def fresh(weights=None, wf=None):
+        g = AdamGroup.create(0, 1, 0, n_half, n_float)
+        w, gr = g.buffers(capi.HALF)
+        wf_, gf = g.buffers(capi.FLOAT)
+        w.view(torch.int16).copy_(dev_u16(W0 if weights is None else weights))
+        wf_.copy_(dev_f32(Wf0 if wf is None else wf))
+        g.init_master(stream_ptr())
+        torch.cuda.synchronize()
+        return g, w, gr, wf_, gf
+
+    def steps(g, gr, gf, scaler, rng):
+        for step in rng:
+            bits = synth.grads_half(n_half, scaler.scale, step, seed=12, inject_inf_every=3)
+            gr.view(torch.int16).copy_(dev_u16(bits))
+            gf.copy_(dev_f32(synth.grads_float(n_float, scaler.scale, step, seed=12)))
+            g.exec(1e-3, 0.01, scaler.scale, stream_ptr())
+            scaler.update(g.flags(stream_ptr()))
+
+    g, w, gr, wf, gf = fresh()
+    sc = LossScaler(128.0)
+    steps(g, gr, gf, sc, range(1, 9))
+    straight = (host_u16(w), wf.cpu().numpy().copy(), [g.export_state(capi.HALF, k) for k in range(3)],
+                [g.export_state(capi.FLOAT, k) for k in range(2)], g.iter, sc.scale)
+    g.destroy()
+
+    g, w, gr, wf, gf = fresh()
+    sc = LossScaler(128.0)
+    steps(g, gr, gf, sc, range(1, 5))
+    g.checkpoint_save(tmp_path, sc.scale, 7)
+    saved_w, saved_wf = host_u16(w), wf.cpu().numpy().copy()
+    g.destroy()
+    names = sorted(os.listdir(tmp_path))
+    assert names == ["adam.r0of1.float.m.saga", "adam.r0of1.float.v.saga", "adam.r0of1.half.m.saga",
+                     "adam.r0of1.half.master.saga", "adam.r0of1.half.v.saga", "adam.r0of1.meta.saga"]
+    m_file = optmod.tensor_load(tmp_path / "adam.r0of1.half.m.saga")
+    assert m_file.dtype == np.float32 and m_file.shape == (n_half,)
+
+    g, w, gr, wf, gf = fresh(saved_w, saved_wf)     # weights come from Saga's own save
+    scale, pstate = g.checkpoint_load(tmp_path)
+    assert pstate == 7 and g.iter == 4
+    sc = LossScaler(scale)
+    steps(g, gr, gf, sc, range(5, 9))
+    assert np.array_equal(host_u16(w), straight[0])
+    assert np.array_equal(wf.cpu().numpy().view(np.uint32), straight[1].view(np.uint32))
+    for k in range(3):
+        assert _bits_equal(g.export_state(capi.HALF, k), straight[2][k])
+    for k in range(2):
+        assert _bits_equal(g.export_state(capi.FLOAT, k), straight[3][k])
+    assert g.iter == straight[4] and sc.scale.tobytes() == straight[5].tobytes()
+    g.destroy()
+
+    other = AdamGroup.create(0, 1, 0, n_half + 16, n_float)
+    try:
+        with pytest.raises(capi.B200OptError):
+            other.checkpoint_load(tmp_path)
+    finally:
+        other.destroy()
+
+
 # ------------------------------------------- several ranks on one GPU (serial mode)
 
 @pytest.mark.parametrize("variant", VARIANTS)
