@@ -343,8 +343,9 @@ class Env:
 def make_group(env, n_half, n_float, want_path):
     """One rank's optimizer wired to its peers; returns (group, path actually used).
     `want_path`: auto | peer | nvls | nccl.  "auto" is the benchmark's own choice: the
-    multicast path where the GPUs offer it and it moves fewer bytes per NVLink
-    direction than the peer path (four ranks and up), the peer path otherwise."""
+    multicast path where the GPUs offer it and it was measured faster than the peer path
+    (eight ranks: 143 against 158 us per step; at four ranks the peer path wins, 137
+    against 146 us, at two it moves fewer bytes to begin with), the peer path otherwise."""
     from saga_b200 import AdamGroup, capi, launch
     flags = 0
     if env.world > 1 and want_path in ("auto", "nvls"):
@@ -355,7 +356,7 @@ def make_group(env, n_half, n_float, want_path):
         info = launch.wire_process_group(grp, with_nccl=True)
     path = want_path
     if want_path == "auto":
-        path = "nvls" if (info["multicast"] and env.world >= 4) else "peer"
+        path = "nvls" if (info["multicast"] and env.world >= 8) else "peer"
     elif want_path == "nvls" and not info["multicast"]:
         path = "peer"
     if env.world == 1:
@@ -730,13 +731,11 @@ def run_tune(args):
     for spec in args.tune.split(","):
         parts = spec.split(":")
         path = parts[0]
-        share = int(parts[1]) if len(parts) > 1 and parts[1] else 0
-        ctas = int(parts[2]) if len(parts) > 2 and parts[2] else 0
-        variant = int(parts[3]) if len(parts) > 3 and parts[3] else 0
+        ctas = int(parts[1]) if len(parts) > 1 and parts[1] else 0
+        variant = int(parts[2]) if len(parts) > 2 and parts[2] else 0
         if path == "nvls" and not info["multicast"]:
             continue
         set_path(grp, path)
-        grp.set_option(capi.OPT_NVLS_PEER_SHARE, share)
         grp.set_option(capi.OPT_CTAS_PER_SM, ctas)
         grp.set_option(capi.OPT_KERNEL_VARIANT, variant)
         fn = lambda: grp.exec(LR, L2, SCALE0, env.sp)   # noqa: E731
@@ -796,8 +795,6 @@ def main():
     ap.add_argument("--variant", type=int, default=-1)
     ap.add_argument("--stages", type=int, default=0)
     ap.add_argument("--grid", type=int, default=0)
-    ap.add_argument("--peer-share", type=int, default=-1,
-                    help="multicast path: trips out of every 8 that take the peer-pointer arithmetic")
     ap.add_argument("--path", default="auto", choices=["auto", "peer", "nvls", "nccl"])
     ap.add_argument("--with-allreduce-baseline", action="store_true",
                     help="N > 1: also time NCCL all-reduce of the whole fp16 gradient buffer followed "
@@ -806,7 +803,7 @@ def main():
                     help="profiling aid: N ranks on ONE GPU, stepped one after the other "
                          "(no cross-GPU waits); times the N-rank kernel against local HBM only")
     ap.add_argument("--tune", default="",
-                    help="tuning aid: comma-separated path[:peer_share[:ctas_per_sm]] settings, each "
+                    help="tuning aid: comma-separated path[:ctas_per_sm[:variant]] settings, each "
                          "timed for --steps steps on the benchmark workload; prints one JSON line")
     ap.add_argument("--sweep", action="store_true", help="config 5: sizes 2^20..2^30 at this N")
     ap.add_argument("--sweep-exps", default="20,22,24,26,28,30")
@@ -874,8 +871,6 @@ def main():
         grp.set_option(capi.OPT_STAGES, args.stages)
     if args.grid:
         grp.set_option(capi.OPT_GRID, args.grid)
-    if args.peer_share >= 0 and path == "nvls":
-        grp.set_option(capi.OPT_NVLS_PEER_SHARE, args.peer_share)
 
     w, g = grp.buffers(capi.FLOAT if f32 else capi.HALF)
     gen = torch.Generator(device=dev).manual_seed(0x5A6A)          # same weights on every rank

@@ -82,9 +82,6 @@ extern "C" {
                                        them in place in the reference), so that a caller can check the
                                        update against the sum it was computed from */
 
-#define B200OPT_OPT_NVLS_PEER_SHARE 11 /* multicast path: k of every 8 trips of a CTA take the peer-pointer
-                                          arithmetic instead of the switch's (0..8, default 0) */
-
 /* creation flags for b200opt_create_ex / b200opt_create_group_ex */
 #define B200OPT_CREATE_FABRIC 1u    /* weight/gradient arena from CUDA's virtual-memory API: shared
                                        between processes as a file descriptor (b200opt_fd_export),

@@ -16,7 +16,6 @@ POLICY_REFERENCE, POLICY_INTERVAL = 0, 1
 PATH_AUTO, PATH_PEER, PATH_NCCL, PATH_NVLS = 0, 1, 2, 3
 OPT_TIMEOUT_MS, OPT_PATH, OPT_CTAS_PER_SM, OPT_KERNEL_VARIANT, OPT_NCCL_CROSSOVER = 1, 2, 3, 4, 5
 OPT_STAGES, OPT_GRID, OPT_PHASE_TIMERS, OPT_ASSUME_NO_PEER_ACCESS, OPT_KEEP_REDUCED = 6, 7, 8, 9, 10
-OPT_NVLS_PEER_SHARE = 11
 KERNEL_DIRECT, KERNEL_STAGED = 1, 2
 CREATE_FABRIC, CREATE_MULTICAST = 1, 2
 MAX_RANKS = 8

@@ -81,7 +81,6 @@ struct b200opt {
     long grid = 0;
     long timing = 0;
     long keep_reduced = 0;
-    long peer_share = 0;
     long assume_no_peer_access = 0;  // test aid: wire as if the GPUs had no peer access
     long nccl_crossover = 0;
     uint64_t launches = 0;
@@ -191,10 +190,7 @@ cudaError_t launch_direct(const StepParams &p, int grid, cudaStream_t st)
 template <int NR>
 cudaError_t launch_nvls(const StepParams &p, int grid, cudaStream_t st)
 {
-    if(p.peer_share > 0)
-        nvls_step_kernel<NR, true, 2><<<grid, kThreads, 0, st>>>(p);
-    else
-        nvls_step_kernel<NR, false, 3><<<grid, kThreads, 0, st>>>(p);
+    nvls_step_kernel<NR, 3><<<grid, kThreads, 0, st>>>(p);
     return cudaGetLastError();
 }
 
@@ -999,7 +995,6 @@ static int step_impl(b200opt_t *h, float lr, float l2_lambda, float scale,
     p.barrier = (h->nranks > 1 && !h->serial) ? 1 : 0;
     if(tune.nvls) {
         p.keep_reduced = h->keep_reduced ? 1 : 0;
-        p.peer_share = (int)h->peer_share;
         p.mcG = reinterpret_cast<const uint16_t *>(h->mc.va + h->off_gh);
         p.mcW = reinterpret_cast<uint16_t *>(h->mc.va + h->off_wh);
     }
@@ -1511,11 +1506,7 @@ int b200opt_set_option(b200opt_t *h, int option, long value)
     case B200OPT_OPT_KEEP_REDUCED:
         h->keep_reduced = value != 0;
         return B200OPT_OK;
-    case B200OPT_OPT_NVLS_PEER_SHARE:
-        if(value < 0 || value > 8)
-            return B200OPT_EINVAL;
-        h->peer_share = value;
-        return B200OPT_OK;
+
     case B200OPT_OPT_ASSUME_NO_PEER_ACCESS:
         if(h->peers_attached > 1)
             return fail(h, B200OPT_ESTATE, "set before any peer is attached");
@@ -1539,7 +1530,6 @@ int b200opt_get_option(const b200opt_t *h, int option, long *value)
     case B200OPT_OPT_GRID: *value = h->grid; return B200OPT_OK;
     case B200OPT_OPT_PHASE_TIMERS: *value = h->timing; return B200OPT_OK;
     case B200OPT_OPT_KEEP_REDUCED: *value = h->keep_reduced; return B200OPT_OK;
-    case B200OPT_OPT_NVLS_PEER_SHARE: *value = h->peer_share; return B200OPT_OK;
     case B200OPT_OPT_ASSUME_NO_PEER_ACCESS:
         *value = h->assume_no_peer_access;
         return B200OPT_OK;

@@ -131,8 +131,6 @@ struct StepParams {
     // (switch-reduced loads, switch-replicated stores); null off that path
     const uint16_t *mcG;
     uint16_t *mcW;
-    int peer_share;         // multicast path: trips out of every 8 that take the
-                            // peer-pointer arithmetic instead (0..8)
 };
 
 // 1/scale of this step: from the launch arguments, or from the scale that

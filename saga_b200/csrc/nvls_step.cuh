@@ -49,12 +49,9 @@ __device__ __forceinline__ void multimem_st_16(void *mc, const uint4 &v)
                  : "memory");
 }
 
-// PEER_MIX: the kernel also carries the peer-pointer arithmetic and runs it on
-// p.peer_share of every 8 trips of a CTA (0 = multicast only).  The switch's
-// reduce and replicate engines and plain peer traffic are separate limits of
-// the fabric; splitting the shard between them moves the step below either
-// one alone.
-template <int NR, bool PEER_MIX, int MINB>
+// Direct loads, one 8-element group per thread per trip; the loads of the first
+// trip's shard state are issued before the wait for the peers.
+template <int NR, int MINB>
 __global__ void __launch_bounds__(kThreads, MINB)
     nvls_step_kernel(const __grid_constant__ StepParams p)
 {
@@ -65,7 +62,7 @@ __global__ void __launch_bounds__(kThreads, MINB)
     const size_t ng = p.h.ngroups;
     const size_t lo = p.h.o, hi = p.h.o + p.h.s;
     size_t base = (size_t)blockIdx.x * kThreads;
-    HalfLoads<PEER_MIX ? NR : 1> L;
+    HalfLoads<1> L;
     bool full = false;
     size_t idx0 = 0;
 
@@ -85,81 +82,29 @@ __global__ void __launch_bounds__(kThreads, MINB)
     }
     if(!step_wait<NR>(p)) {
         const float alpha = step_alpha(p);
-        for(size_t trip = 0; base < ng; base += stride, trip++) {
+        for(; base < ng; base += stride) {
             if(!state_loaded) {
                 classify(base);
                 if(full)
                     half_load_state(p, idx0, L);
             }
             state_loaded = false;
-            // the same choice in every thread of the CTA and on every rank
-            const bool via_peers =
-                PEER_MIX && (int)((blockIdx.x + trip) & 7u) < p.peer_share;
             if(full) {
-                if(via_peers) {
-                    if(PEER_MIX) {
-                        half_load_grads<PEER_MIX ? NR : 1>(p, idx0, L);
-                        uint4 out[7];
-                        half_compute<PEER_MIX ? NR : 1>(p, alpha, idx0, L, fl, out);
-                        const size_t li = idx0 - p.h.A;
-                        st_stream(p.h.m + li, out[0]);
-                        st_stream(p.h.m + li + 4, out[1]);
-                        st_stream(p.h.v + li, out[2]);
-                        st_stream(p.h.v + li + 4, out[3]);
-                        st_stream(p.h.c + li, out[4]);
-                        st_stream(p.h.c + li + 4, out[5]);
-#pragma unroll
-                        for(int q = 0; q < NR; q++)
-                            *reinterpret_cast<uint4 *>(p.h.W[q] + idx0) = out[6];
-                        if(p.keep_reduced) {
-                            // the rank-ordered sum this arm formed, recomputed for the record
-                            uint32_t u[8];
-                            float acc[8];
-                            halves8(L.g[0], u);
-#pragma unroll
-                            for(int e = 0; e < 8; e++)
-                                acc[e] = half_bits_to_float(u[e]);
-#pragma unroll
-                            for(int q = 1; q < (PEER_MIX ? NR : 1); q++) {
-                                uint32_t t8[8];
-                                halves8(L.g[q], t8);
-#pragma unroll
-                                for(int e = 0; e < 8; e++)
-                                    acc[e] += half_bits_to_float(t8[e]);
-                            }
-#pragma unroll
-                            for(int e = 0; e < 8; e++)
-                                u[e] = float_to_half_bits(acc[e]);
-                            *reinterpret_cast<uint4 *>(
-                                const_cast<uint16_t *>(p.h.G[p.rank]) + idx0) =
-                                make_uint4(u[0] | (u[1] << 16), u[2] | (u[3] << 16),
-                                           u[4] | (u[5] << 16), u[6] | (u[7] << 16));
-                        }
-                    }
-                } else {
-                    HalfLoads<1> S;
-                    S.g[0] = multimem_ld_reduce_f16x8(p.mcG + idx0);
-                    S.m0 = L.m0;
-                    S.m1 = L.m1;
-                    S.v0 = L.v0;
-                    S.v1 = L.v1;
-                    S.c0 = L.c0;
-                    S.c1 = L.c1;
-                    uint4 out[7];
-                    // the sum is already formed: the one-rank arithmetic
-                    half_compute<1>(p, alpha, idx0, S, fl, out);
-                    const size_t li = idx0 - p.h.A;
-                    st_stream(p.h.m + li, out[0]);
-                    st_stream(p.h.m + li + 4, out[1]);
-                    st_stream(p.h.v + li, out[2]);
-                    st_stream(p.h.v + li + 4, out[3]);
-                    st_stream(p.h.c + li, out[4]);
-                    st_stream(p.h.c + li + 4, out[5]);
-                    multimem_st_16(p.mcW + idx0, out[6]);
-                    if(p.keep_reduced)
-                        *reinterpret_cast<uint4 *>(
-                            const_cast<uint16_t *>(p.h.G[p.rank]) + idx0) = S.g[0];
-                }
+                L.g[0] = multimem_ld_reduce_f16x8(p.mcG + idx0);
+                uint4 out[7];
+                // the sum is already formed: the one-rank arithmetic
+                half_compute<1>(p, alpha, idx0, L, fl, out);
+                const size_t li = idx0 - p.h.A;
+                st_stream(p.h.m + li, out[0]);
+                st_stream(p.h.m + li + 4, out[1]);
+                st_stream(p.h.v + li, out[2]);
+                st_stream(p.h.v + li + 4, out[3]);
+                st_stream(p.h.c + li, out[4]);
+                st_stream(p.h.c + li + 4, out[5]);
+                multimem_st_16(p.mcW + idx0, out[6]);
+                if(p.keep_reduced)
+                    *reinterpret_cast<uint4 *>(
+                        const_cast<uint16_t *>(p.h.G[p.rank]) + idx0) = L.g[0];
             } else if(base + tid < ng && idx0 + kVec > lo) {
                 fl |= half_scalar<NR>(p, alpha, idx0);
             }

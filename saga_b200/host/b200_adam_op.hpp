@@ -25,6 +25,8 @@
 // way it reports any failing op (src/cuda/cuda_program.cpp:226-231).
 #pragma once
 
+#include <algorithm>
+#include <chrono>
 #include <condition_variable>
 #include <functional>
 #include <map>
@@ -39,42 +41,104 @@ namespace saga {
 
 // Meeting point of the rank threads of one engine.  Every rank creates its own
 // handle on its own device, then joins; join() returns when all ranks have
-// joined and this rank has attached every peer.
+// joined and this rank has attached every peer.  A rank whose program has
+// nothing to train still joins, with a null handle, so that nobody waits for it
+// in vain; the wait itself is bounded and names the ranks that did not come.
+// The object serves one program after the other: when the last rank of a round
+// has left, the counters and the handle table start over.
 class B200Rendezvous {
 public:
-    explicit B200Rendezvous(int nranks) : m_handles(nranks, nullptr) {}
+    explicit B200Rendezvous(int nranks, int timeout_seconds = 120)
+      : m_handles(nranks, nullptr), m_present(nranks, false), m_timeout_s(timeout_seconds)
+    {
+    }
 
     void join(int rank, b200opt_t *h)
     {
         const int n = (int)m_handles.size();
+        std::vector<b200opt_t *> peers;
         {
             std::unique_lock<std::mutex> lock(m_mutex);
+            // a new round only starts once the previous one has been left by all
+            wait_or_throw(lock, [&] { return m_leaving == 0; }, "the previous round to end");
             m_handles[rank] = h;
+            m_present[rank] = true;
             m_joined++;
             m_cond.notify_all();
-            m_cond.wait(lock, [&] { return m_joined >= n; });
+            try {
+                wait_or_throw(lock, [&] { return m_joined >= n; }, "every rank to join");
+            } catch(...) {
+                // take this rank out again: a later attempt starts from a clean table
+                m_handles[rank] = nullptr;
+                m_present[rank] = false;
+                m_joined--;
+                throw;
+            }
+            peers = m_handles;
         }
-        for(int q = 0; q < n; q++) {
-            if(q == rank)
-                continue;
-            const int rc = b200opt_attach_local(h, q, m_handles[q]);
-            if(rc != B200OPT_OK)
-                throw std::runtime_error(std::string("b200opt_attach_local: ") +
-                                         b200opt_last_error(h));
+        std::string err;
+        if(h) {
+            for(int q = 0; q < n && err.empty(); q++) {
+                if(q == rank)
+                    continue;
+                if(!peers[q])
+                    err = "rank " + std::to_string(q) + " has no trainable tensors but rank " +
+                          std::to_string(rank) + " has";
+                else if(b200opt_attach_local(h, q, peers[q]) != B200OPT_OK)
+                    err = std::string("b200opt_attach_local: ") + b200opt_last_error(h);
+            }
         }
-        // nobody may step before every rank has wired its peers
+        // nobody may step before every rank has wired its peers; the last rank
+        // out resets the object for the next program
         std::unique_lock<std::mutex> lock(m_mutex);
         m_wired++;
         m_cond.notify_all();
-        m_cond.wait(lock, [&] { return m_wired >= n; });
+        try {
+            wait_or_throw(lock, [&] { return m_wired >= n; }, "every rank to wire its peers");
+        } catch(...) {
+            leave(n);
+            throw;
+        }
+        leave(n);
+        if(!err.empty())
+            throw std::runtime_error(err);
     }
 
 private:
+    // called with the mutex held, by every rank once, on its way out of a round
+    void leave(int n)
+    {
+        if(m_leaving == 0)
+            m_leaving = n;
+        if(--m_leaving == 0) {
+            m_joined = m_wired = 0;
+            std::fill(m_handles.begin(), m_handles.end(), nullptr);
+            std::fill(m_present.begin(), m_present.end(), false);
+            m_cond.notify_all();
+        }
+    }
+
+    template <typename Pred>
+    void wait_or_throw(std::unique_lock<std::mutex> &lock, Pred pred, const char *what)
+    {
+        if(m_cond.wait_for(lock, std::chrono::seconds(m_timeout_s), pred))
+            return;
+        std::string missing;
+        for(size_t q = 0; q < m_present.size(); q++)
+            if(!m_present[q])
+                missing += (missing.empty() ? "" : ", ") + std::to_string(q);
+        throw std::runtime_error(std::string("b200opt rendezvous: gave up waiting for ") + what +
+                                 (missing.empty() ? "" : " (ranks not seen: " + missing + ")"));
+    }
+
     std::mutex m_mutex;
     std::condition_variable m_cond;
     std::vector<b200opt_t *> m_handles;
+    std::vector<bool> m_present;
+    int m_timeout_s;
     int m_joined = 0;
     int m_wired = 0;
+    int m_leaving = 0;
 };
 
 #ifdef HAVE_B200OPT  // the part below needs Saga's own headers

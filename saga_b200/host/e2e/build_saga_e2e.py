@@ -3,6 +3,7 @@
   _build/saga_e2e_ref    the reference library, unmodified (NCCL build),
                          + its own test/test_classifier.cpp + e2e_main.cpp
   _build/saga_cifar18_*  the same two library builds + e2e_cifar_resnet18.cpp
+  _build/saga_parity_*   the same two library builds + e2e_parity.cpp
   _build/saga_e2e_b200   the same with the optimizer ops replaced by the
                          b200opt op: the library sources are copied to a
                          scratch directory outside this repository and
@@ -66,7 +67,16 @@ def patch_tree(tree):
     def storage_cpp(t):
         a = "chkCuda(cudaFree(m_mem));"
         assert a in t
-        return t.replace(a, "if(!m_external)\n        " + a, 1)
+        t = t.replace(a, "if(!m_external)\n        " + a, 1)
+        # host access to tensors in library-owned device memory goes through a staging copy
+        b = "std::unique_ptr<TensorAccess>\nCudaTensor::access()"
+        assert b in t
+        t = t.replace(b, '#include <vector>\n#include <cstring>\n#include "b200_tensor_access.inc"\n\n' + b, 1)
+        c = "return std::make_unique<CudaTensorAccess>(m_storage, m_desc, m_offset);"
+        assert t.count(c) == 1
+        return t.replace(c, "if(m_storage->m_memory && m_storage->m_memory->m_external)\n"
+                            "        return std::make_unique<B200StagedTensorAccess>(m_storage, m_desc, "
+                            "m_offset);\n    " + c, 1)
 
     def optimizer_cpp(t):
         start = t.index("CudaOps\nCudaProgram::create_optimizers()")
@@ -105,6 +115,8 @@ def build_variant(ref, work, name, defines, extra_inc, extra_libs):
     run(CXX + defines + inc + ["-c", os.path.join(HERE, "e2e_main.cpp"), "-o", mobj])
     cobj = os.path.join(work, name + "_cifar.o")
     run(CXX + defines + inc + ["-c", os.path.join(HERE, "e2e_cifar_resnet18.cpp"), "-o", cobj])
+    pobj = os.path.join(work, name + "_parity.o")
+    run(CXX + defines + inc + ["-c", os.path.join(HERE, "e2e_parity.cpp"), "-o", pobj])
     for p in procs:
         out, _ = p.communicate()
         if p.returncode != 0:
@@ -117,7 +129,10 @@ def build_variant(ref, work, name, defines, extra_inc, extra_libs):
     # the CIFAR-variant ResNet-18 program uses the public API only
     exe2 = os.path.join(OUT, name.replace("saga_e2e", "saga_cifar18"))
     run(["g++", "-o", exe2] + lib_objs + [kobj, cobj] + LIBS + extra_libs)
-    return exe + " " + exe2
+    # the parity program: identical injected weights, scale log and trained weights on disk
+    exe3 = os.path.join(OUT, name.replace("saga_e2e", "saga_parity"))
+    run(["g++", "-o", exe3] + lib_objs + [kobj, pobj] + LIBS + extra_libs)
+    return " ".join((exe, exe2, exe3))
 
 
 def main():

@@ -1,0 +1,118 @@
+// Parity of a whole Saga training run between the unmodified library and the
+// library with the b200opt optimizer op, through Saga's public API only
+// (saga.hpp): a small mixed-precision classifier -- fc, batch-norm, relu, fc,
+// softmax classifier; fp16 activations and weights with fp32 master copies,
+// fp32 batch-norm parameters, so both dtype groups of the optimizer are in
+// play -- trained step by step on one GPU with fixed inputs.
+//
+//   saga_parity init  <dir>                 writes the model's initial tensors
+//                                           (Saga's own random init) to <dir>
+//   saga_parity train <dir_in> <dir_out> <steps>
+//                                           loads the tensors of <dir_in>, trains
+//                                           <steps> batches, saves the trained
+//                                           tensors to <dir_out> (Graph::saveTensors,
+//                                           i.e. through host tensor access), prints
+//                                           one JSON line: the loss scale after every
+//                                           step (bit patterns) and the mean loss
+//
+// Linked against both library builds (build_saga_e2e.py); the test runs "init"
+// once and "train" with each and compares what they leave.
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "saga.hpp"
+
+using namespace saga;
+
+int main(int argc, char **argv)
+{
+    if(argc < 3) {
+        fprintf(stderr, "usage: %s init <dir> | train <dir_in> <dir_out> <steps>\n", argv[0]);
+        return 2;
+    }
+    const bool init = !strcmp(argv[1], "init");
+    const int steps = (!init && argc > 4) ? atoi(argv[4]) : 0;
+    const int batch_size = 64, hw = 16, classes = 10;
+    const auto dt = Tensor::DataType::HALF;
+
+    Graph g;
+    if(!init)
+        g.loadTensors(argv[2]);  // found by name when the nodes below are created
+
+    auto x = makeTensor(Tensor::DataType::U8, Dims({1, 1, hw, hw}), "input");
+    auto n = g.addConvert(x, dt, 1.0f / 255.0f);
+    n = g.addNode("fc", n->y(), {{"outputs", 96}, {"bias", true}}, "fc1");
+    n = g.addNode("batchnorm", n->y(), {}, "bn1");
+    n = g.addNode("relu", n->y());
+    n = g.addNode("fc", n->y(), {{"outputs", classes}, {"bias", true}}, "fc2");
+    n = g.addNode("catclassifier", n->y());
+
+    const auto LABELS = n->m_outputs["y"]->grad();
+    const auto LOSS = n->m_outputs["loss"];
+    const BatchedTensors bt{{LOSS, Phase::POST}, {LABELS, Phase::PRE}, {x, Phase::PRE}};
+
+    // deterministic inputs: one byte pattern per batch index
+    double loss_sum = 0;
+    long loss_cnt = 0;
+    auto pre_ops = [&](long batch, const Program &, auto tas) {
+        std::vector<uint8_t> pixels((size_t)batch_size * hw * hw);
+        uint32_t s = 1234567u + (uint32_t)batch * 7919u;
+        for(auto &p : pixels) {
+            s = s * 1664525u + 1013904223u;
+            p = (uint8_t)(s >> 24);
+        }
+        tas[x]->copyBytesFrom({}, pixels.data(), pixels.size());
+        auto &labels = *tas[LABELS];
+        for(int i = 0; i < batch_size; i++)
+            labels.set({i}, (int)(((uint32_t)(batch * batch_size + i) * 2654435761u) >> 28) % classes);
+    };
+    auto post_ops = [&](long, const Program &, auto tas) {
+        auto &loss = *tas[LOSS];
+        for(int i = 0; i < batch_size; i++)
+            loss_sum += loss.get({i});
+        loss_cnt += batch_size;
+    };
+
+    auto engine = createEngine(make_nui());
+    auto contexts = engine->createContexts(false);
+    auto &ctx = contexts[0];
+    const ProgramConfig pc{.pre_ops = pre_ops,
+                           .post_ops = post_ops,
+                           .learning_rate = 1e-3,
+                           .l2_lambda = 0.01,
+                           .tensor_layout = TensorLayout::NHWC};
+    const ProgramSource ps{.graph = g, .batched_tensors = bt, .batch_size = batch_size};
+    auto training = ctx->createProgram(ps, ProgramType::TRAINING, pc);
+    training->finalize();
+
+    if(init) {
+        if(!g.saveTensors(argv[2], ctx.get())) {
+            fprintf(stderr, "could not save the initial tensors to %s\n", argv[2]);
+            return 1;
+        }
+        printf("{\"parity\": \"init\", \"dir\": \"%s\"}\n", argv[2]);
+        return 0;
+    }
+
+    std::vector<float> scales;
+    for(int s = 0; s < steps; s++) {
+        training->run(1, nullptr, s);
+        scales.push_back(training->getMPS());
+    }
+    if(!g.saveTensors(argv[3], ctx.get())) {
+        fprintf(stderr, "could not save the trained tensors to %s\n", argv[3]);
+        return 1;
+    }
+    printf("\n{\"parity\": \"train\", \"steps\": %d, \"loss_mean\": %.6f, \"scale_bits\": [", steps,
+           loss_cnt ? loss_sum / loss_cnt : 0.0);
+    for(size_t i = 0; i < scales.size(); i++) {
+        uint32_t bits;
+        memcpy(&bits, &scales[i], 4);
+        printf("%s%u", i ? ", " : "", bits);
+    }
+    printf("]}\n");
+    return 0;
+}

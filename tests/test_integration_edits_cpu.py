@@ -37,7 +37,13 @@ def test_anchored_edits_apply_to_the_checkout(tmp_path):
     assert prog.count("b200_fill_aux(*this);") == 1
     assert prog.index("b200_fill_aux(*this);") < prog.index("m_mp_scaling *= 0.5")
     assert "bool m_external{false};" in (tree / "src" / "cuda" / "cuda_tensor.hpp").read_text()
-    assert "if(!m_external)" in (tree / "src" / "cuda" / "cuda_tensor.cpp").read_text()
+    tensor_cpp = (tree / "src" / "cuda" / "cuda_tensor.cpp").read_text()
+    assert "if(!m_external)" in tensor_cpp
+    # host access to library-owned device memory is staged
+    assert tensor_cpp.count('#include "b200_tensor_access.inc"') == 1
+    assert tensor_cpp.index('#include "b200_tensor_access.inc"') < tensor_cpp.index("CudaTensor::access()")
+    assert "std::make_unique<B200StagedTensorAccess>(m_storage, m_desc, m_offset)" in tensor_cpp
+    assert tensor_cpp.count("std::make_unique<CudaTensorAccess>(m_storage, m_desc, m_offset)") == 1
 
 
 def test_integration_sources_name_every_entry_point_they_use():

@@ -51,7 +51,7 @@ def _multicast_or_skip(ndev):
         pytest.skip("these GPUs do not support NVSwitch multicast")
 
 
-def _run_multicast_trajectory(oracle, nranks, n_half, n_float, steps, seed, peer_share=0):
+def _run_multicast_trajectory(oracle, nranks, n_half, n_float, steps, seed):
     """The multicast path against the oracle, the way its arithmetic allows:
 
     * the switch's fp16 sum lands within one fp16 ulp of the correctly rounded
@@ -67,7 +67,6 @@ def _run_multicast_trajectory(oracle, nranks, n_half, n_float, steps, seed, peer
                    create_flags=capi.CREATE_MULTICAST)
     for g in prog.groups:
         g.set_option(capi.OPT_KEEP_REDUCED, 1)
-        g.set_option(capi.OPT_NVLS_PEER_SHARE, peer_share)
     prog.set_weights([W0] * nranks, [Wf0] * nranks if n_float else None)
     ost = oracle.MultiRankState(nranks, [W0] * nranks, [Wf0] * nranks if n_float else None)
     gs = LossScaler(64.0)
@@ -115,8 +114,7 @@ def test_two_gpus_multicast_path(oracle):
     _multicast_or_skip(2)
     for n_half, n_float in ((16, 16), (8208, 528), (2048 * 7 * 2 + 80, 0)):
         _run_multicast_trajectory(oracle, 2, n_half, n_float, 6, seed=85)
-    # part of the shard through the peer pointers, part through the switch
-    _run_multicast_trajectory(oracle, 2, 2048 * 40 * 2 + 80, 0, 4, seed=88, peer_share=3)
+    _run_multicast_trajectory(oracle, 2, 2048 * 40 * 2 + 80, 0, 4, seed=88)
 
 
 def test_multicast_path_needs_its_object(oracle):
@@ -139,7 +137,7 @@ def test_all_gpus_multicast_path(oracle):
     n = 8 if n >= 8 else 4
     _multicast_or_skip(n)
     _run_multicast_trajectory(oracle, n, 2048 * 5 * n + 16, 528, 6, seed=86)
-    _run_multicast_trajectory(oracle, n, 2048 * 40 * n + 16, 0, 3, seed=89, peer_share=2)
+    _run_multicast_trajectory(oracle, n, 2048 * 40 * n + 16, 0, 3, seed=89)
 
 
 def test_all_gpus_one_process_matches_oracle(oracle):
