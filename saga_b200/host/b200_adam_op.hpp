@@ -164,6 +164,13 @@ struct B200Adam : public CudaOperation {
     {
         if(m_on_destroy)
             m_on_destroy();  // lets the owner forget the handle first
+        if(m_timed_steps)
+            fprintf(stderr, "{\"b200_adam_op\": {\"rank\": %d, \"steps\": %ld, \"mean_us\": %.2f}}\n",
+                    m_ctx->m_nccl_rank, m_timed_steps, 1e3 * m_timed_ms / m_timed_steps);
+        if(m_ev[0]) {
+            cudaEventDestroy(m_ev[0]);
+            cudaEventDestroy(m_ev[1]);
+        }
         b200opt_destroy(m_handle);
     }
 
@@ -172,12 +179,41 @@ struct B200Adam : public CudaOperation {
     // update, all-gather -- all inside b200opt_step.  Asynchronous.
     void exec(CudaProgram &p) override
     {
+        // B200OPT_TIME_OP=1: device time of the op, one event on each side of it,
+        // read in note_step_done() after the step's stream synchronise
+        if(m_timing < 0) {
+            const char *e = getenv("B200OPT_TIME_OP");
+            m_timing = e && atoi(e) ? 1 : 0;
+            if(m_timing) {
+                cudaEventCreate(&m_ev[0]);
+                cudaEventCreate(&m_ev[1]);
+            }
+        }
+        if(m_timing)
+            cudaEventRecord(m_ev[0], p.m_ctx->m_stream);
         const int rc = b200opt_step(m_handle, p.m_pc.learning_rate,
                                     p.m_pc.l2_lambda, p.m_mp_scaling,
                                     p.m_ctx->m_stream);
         if(rc != B200OPT_OK)
             throw std::runtime_error(std::string("b200opt_step: ") +
                                      b200opt_last_error(m_handle));
+        if(m_timing) {
+            cudaEventRecord(m_ev[1], p.m_ctx->m_stream);
+            m_pending = true;
+        }
+    }
+
+    // called once the stream has been synchronised after a step
+    void note_step_done()
+    {
+        if(!m_pending)
+            return;
+        m_pending = false;
+        float ms = 0;
+        if(cudaEventElapsedTime(&ms, m_ev[0], m_ev[1]) == cudaSuccess) {
+            m_timed_ms += ms;
+            m_timed_steps++;
+        }
     }
 
     // Replaces the flag block at the end of CudaProgram::step
@@ -200,6 +236,11 @@ struct B200Adam : public CudaOperation {
     CudaOpArgs listOutputs() const override { return m_outputs; }
 
     b200opt_t *m_handle;
+    int m_timing = -1;
+    bool m_pending = false;
+    cudaEvent_t m_ev[2] = {nullptr, nullptr};
+    double m_timed_ms = 0;
+    long m_timed_steps = 0;
     std::function<void()> m_on_destroy;
     CudaOpArgs m_inputs;
     CudaOpArgs m_outputs;

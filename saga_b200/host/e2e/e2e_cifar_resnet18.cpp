@@ -35,7 +35,7 @@ int main(int argc, char **argv)
     const auto dt = Tensor::DataType::HALF;
 
     Graph g;
-    auto x = makeTensor(Tensor::DataType::U8, Dims({1, 3, 32, 32}), "input");
+    auto x = makeTensor(Tensor::DataType::U8, Dims({DimParam::BATCH_SIZE, 3, 32, 32}), "input");
     auto n = g.addConvert(x, dt, 1.0f / 255.0f);
     n = g.addNode("conv", n->y(),
                   {{"size", 3}, {"activations", 64}, {"stride", 1}, {"pad", 1}}, "stem-conv");

@@ -64,7 +64,7 @@ int main(int argc, char **argv)
         p = (uint8_t)(s >> 24);
     }
 
-    auto input = makeTensor(Tensor::DataType::U8, Dims({1, 3, hw, hw}), "input");
+    auto input = makeTensor(Tensor::DataType::U8, Dims({DimParam::BATCH_SIZE, 3, hw, hw}), "input");
 
     std::vector<double> train_begin, train_end;
     int bs_seen = 0;

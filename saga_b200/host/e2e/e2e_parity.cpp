@@ -1,9 +1,10 @@
 // Parity of a whole Saga training run between the unmodified library and the
 // library with the b200opt optimizer op, through Saga's public API only
-// (saga.hpp): a small mixed-precision classifier -- fc, batch-norm, relu, fc,
+// (saga.hpp): a small mixed-precision classifier -- fc, relu, fc, relu, fc,
 // softmax classifier; fp16 activations and weights with fp32 master copies,
-// fp32 batch-norm parameters, so both dtype groups of the optimizer are in
-// play -- trained step by step on one GPU with fixed inputs.
+// cuBLAS only (no convolution, whose algorithm cuDNN picks by timing and which
+// would make two runs differ by themselves) -- trained step by step on one GPU
+// with fixed inputs.
 //
 //   saga_parity init  <dir>                 writes the model's initial tensors
 //                                           (Saga's own random init) to <dir>
@@ -42,12 +43,13 @@ int main(int argc, char **argv)
     if(!init)
         g.loadTensors(argv[2]);  // found by name when the nodes below are created
 
-    auto x = makeTensor(Tensor::DataType::U8, Dims({1, 1, hw, hw}), "input");
+    auto x = makeTensor(Tensor::DataType::U8, Dims({DimParam::BATCH_SIZE, 1, hw, hw}), "input");
     auto n = g.addConvert(x, dt, 1.0f / 255.0f);
     n = g.addNode("fc", n->y(), {{"outputs", 96}, {"bias", true}}, "fc1");
-    n = g.addNode("batchnorm", n->y(), {}, "bn1");
     n = g.addNode("relu", n->y());
-    n = g.addNode("fc", n->y(), {{"outputs", classes}, {"bias", true}}, "fc2");
+    n = g.addNode("fc", n->y(), {{"outputs", 48}, {"bias", true}}, "fc2");
+    n = g.addNode("relu", n->y());
+    n = g.addNode("fc", n->y(), {{"outputs", classes}, {"bias", true}}, "fc3");
     n = g.addNode("catclassifier", n->y());
 
     const auto LABELS = n->m_outputs["y"]->grad();

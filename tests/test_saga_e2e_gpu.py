@@ -1,6 +1,6 @@
 """A whole Saga training run, unmodified library against the library with the b200opt
 optimizer op: same injected initial tensors, same inputs, 20 steps of a small
-mixed-precision classifier on one GPU.  The loss-scale trajectory must be identical bit
+mixed-precision classifier (three fc layers, fp16 with fp32 master copies) on one GPU.  The loss-scale trajectory must be identical bit
 for bit and every trained tensor (read back through Saga's own host tensor access and
 tensor files) must agree within 1e-5.  Skipped where the two programs were not built
 (they need the Saga checkout at build time: saga_b200/host/e2e/build_saga_e2e.py)."""
@@ -36,7 +36,7 @@ def test_integrated_build_trains_like_the_unmodified_one(tmp_path):
     init, out_ref, out_b200 = tmp_path / "init", tmp_path / "ref", tmp_path / "b200"
     _run(REF, "init", init)
     names = sorted(os.listdir(init))
-    assert any(n.startswith("fc1") for n in names) and any(n.startswith("bn1") for n in names)
+    assert {"fc1-w", "fc2-w", "fc3-w"} <= set(names)
     a = _run(REF, "train", init, out_ref, steps)
     b = _run(B200, "train", init, out_b200, steps)
     assert a["steps"] == b["steps"] == steps
@@ -45,14 +45,19 @@ def test_integrated_build_trains_like_the_unmodified_one(tmp_path):
     assert len(set(a["scale_bits"])) == steps
     assert abs(a["loss_mean"] - b["loss_mean"]) <= 1e-4 * max(1.0, abs(a["loss_mean"]))
     assert sorted(os.listdir(out_ref)) == sorted(os.listdir(out_b200)) == names
-    moved = 0
+    moved = []
     for name in names:
         x0 = opt.tensor_load(init / name).astype(np.float64)
         xr = opt.tensor_load(out_ref / name).astype(np.float64)
         xb = opt.tensor_load(out_b200 / name).astype(np.float64)
         assert xr.shape == xb.shape == x0.shape, name
-        rms = np.sqrt(np.mean(xr * xr)) if xr.size else 0.0
-        err = np.max(np.abs(xb - xr) / (np.abs(xr) + rms + 1e-30)) if xr.size else 0.0
-        assert err <= 1e-5, (name, err)
-        moved += int(np.any(xr != x0))
-    assert moved >= 4, "training did not change the weights"
+        fin = np.isfinite(xr)
+        assert np.array_equal(fin, np.isfinite(xb)), name
+        if fin.any():
+            rms = np.sqrt(np.mean(xr[fin] ** 2))
+            err = np.max(np.abs(xb[fin] - xr[fin]) / (np.abs(xr[fin]) + rms + 1e-30))
+            assert err <= 1e-5, (name, err)
+        if np.any(xr[fin] != x0[fin]):
+            moved.append(name)
+    # training changed the weights of every layer
+    assert {"fc1-w", "fc2-w", "fc3-w"} <= set(moved), f"training changed only {moved} of {names}"
