@@ -117,6 +117,36 @@ def test_two_gpus_multicast_path(oracle):
     _run_multicast_trajectory(oracle, 2, 2048 * 40 * 2 + 80, 0, 4, seed=88)
 
 
+def test_what_the_switch_computes(tmp_path):
+    """The measured properties of multimem.ld_reduce that the multicast path's parity rule
+    rests on (tests/nvls_probe.cu): on f16x2 the switch's sum is deterministic, the same with
+    and without .acc::f32, never more than one fp16 ulp from the correctly rounded sum -- but
+    one ulp off for a good part of the values; on f32 it is the correctly rounded sum."""
+    n = _ngpu()
+    n = 8 if n >= 8 else (4 if n >= 4 else 2)
+    _multicast_or_skip(n)
+    exe = tmp_path / "nvls_probe"
+    res = subprocess.run(["nvcc", "-std=c++17", "-O2", "-gencode", "arch=compute_100a,code=sm_100a",
+                          "-I", os.path.join(ROOT, "include"),
+                          os.path.join(ROOT, "tests", "nvls_probe.cu"),
+                          os.path.join(ROOT, "saga_b200", "csrc", "fabric.cpp"), "-o", str(exe)],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-3000:]
+    res = subprocess.run([str(exe), str(n)], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    rows = [json.loads(ln) for ln in res.stdout.splitlines() if ln.startswith("{")]
+    print("\n".join(json.dumps(r) for r in rows))          # shown with pytest -s / on failure
+    by = {r["form"]: r for r in rows}
+    plain, acc, f32 = by["f16x2"], by["f16x2 acc::f32"], by["f32"]
+    for r in (plain, acc):
+        assert r["differ_between_runs"] == 0 and r["beyond"] == 0
+        h = r["ulps_minus4_to_plus4"]
+        assert sum(h[:3]) == 0 and sum(h[6:]) == 0          # never more than one ulp
+        assert 0.05 * r["values"] < h[3] + h[5] < 0.5 * r["values"]   # but often one
+    assert plain["ulps_minus4_to_plus4"] == acc["ulps_minus4_to_plus4"]
+    assert f32["differ_from_correctly_rounded_sum"] == 0
+
+
 def test_multicast_path_needs_its_object(oracle):
     prog = Program(2, 4096, devices=[0, 1], path=capi.PATH_NVLS)
     try:
