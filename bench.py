@@ -350,7 +350,19 @@ def make_group(env, n_half, n_float, want_path):
     flags = 0
     if env.world > 1 and want_path in ("auto", "nvls"):
         flags = capi.CREATE_MULTICAST
-    grp = AdamGroup.create(env.rank, env.world, env.local, n_half, n_float, flags)
+    grp = None
+    if flags:
+        # every rank must end up with the same kind of arena: fall back together
+        try:
+            grp = AdamGroup.create(env.rank, env.world, env.local, n_half, n_float, flags)
+        except capi.B200OptError:
+            grp = None
+        if not env.all_true(grp is not None):
+            if grp is not None:
+                grp.destroy()
+            grp, flags = None, 0
+    if grp is None:
+        grp = AdamGroup.create(env.rank, env.world, env.local, n_half, n_float, 0)
     info = {"multicast": False}
     if env.world > 1:
         info = launch.wire_process_group(grp, with_nccl=True)

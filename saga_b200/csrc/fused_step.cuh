@@ -806,7 +806,8 @@ __device__ __forceinline__ void step_finish(const StepParams &p, uint32_t fl,
         }
         my->local_flags = 0;
         my->cta_done = 0;
-        __threadfence_system();
+        // no fence: the end of the kernel makes these stores visible to the host
+        // and to the next launch on the stream
     }
 }
 
