@@ -299,6 +299,15 @@ B200OPT_API int b200opt_step_host(b200opt_t *h, const void *grads_half,
  *                              and the log of the last `log_capacity` steps,
  *                              oldest first, four words per step:
  *                              {range, inf, nan, bits of the scale after it}
+ *   b200opt_device_scale_peek  does not wait and makes no CUDA call: the scale
+ *                              after the last step whose kernel has FINISHED
+ *                              (the kernel leaves it in the pinned result
+ *                              page) and that step's number; the initial
+ *                              scale and 0 before any step has finished.  For
+ *                              a host that paces itself with events one step
+ *                              behind the device and wants a scale to show
+ *                              (the UI cell of src/cuda/cuda_program.cpp:316)
+ *                              without draining the stream.
  * Not available in serial mode or on the NCCL path.
  */
 B200OPT_API int b200opt_device_scale_enable(b200opt_t *h, float initial_scale,
@@ -310,6 +319,8 @@ B200OPT_API int b200opt_step_device_scale(b200opt_t *h, float lr,
 B200OPT_API int b200opt_device_scale_read(b200opt_t *h, void *stream,
                                           float *scale, uint32_t *log_out,
                                           size_t capacity, size_t *count);
+B200OPT_API int b200opt_device_scale_peek(b200opt_t *h, float *scale,
+                                          uint32_t *step);
 
 /*
  * Waits for `stream`, then returns the sums over ranks of {range, inf, nan}

@@ -59,6 +59,7 @@ SIGNATURES = {
     "b200opt_device_scale_ptr": (_i, [_vp, C.POINTER(_vp)]),
     "b200opt_step_device_scale": (_i, [_vp, _f, _f, _vp]),
     "b200opt_device_scale_read": (_i, [_vp, _vp, _fp, _vp, _sz, C.POINTER(_sz)]),
+    "b200opt_device_scale_peek": (_i, [_vp, _fp, _u32p]),
     "b200opt_policy_update": (_i, [_fp, _u32p, _i, C.POINTER(_i), _i]),
     "b200opt_bias_corrections": (_i, [_i, _fp, _fp]),
     "b200opt_choose_path": (_i, [_i, _i, _i, _i, _i, _i, _sz, _sz, C.POINTER(_i)]),

@@ -86,6 +86,7 @@ struct b200opt {
     uint64_t launches = 0;
     NcclPath *nccl = nullptr;
     bool device_scale = false;   // loss scale lives in the control page
+    float device_scale_initial = 0;
     bool step_open = false;      // between b200opt_step_begin and the last bucket
     uint32_t *scale_log = nullptr;
     uint32_t scale_log_cap = 0;
@@ -1093,6 +1094,8 @@ int b200opt_device_scale_enable(b200opt_t *h, float initial_scale, int policy,
                   "device scale fields are contiguous");
     CK(h, cudaMemcpy(&ctrl->scale, &init, sizeof(init), cudaMemcpyHostToDevice));
     h->device_scale = true;
+    h->device_scale_initial = initial_scale;
+    h->host->scale_bits = 0;
     return B200OPT_OK;
 }
 
@@ -1104,6 +1107,31 @@ int b200opt_device_scale_ptr(b200opt_t *h, const float **scale_dev)
         return fail(h, B200OPT_ESTATE,
                     "b200opt_device_scale_enable has not been called");
     *scale_dev = &arena_ptr<Ctrl>(h->arena, 0)->scale;
+    return B200OPT_OK;
+}
+
+int b200opt_device_scale_peek(b200opt_t *h, float *scale, uint32_t *step)
+{
+    if(!h)
+        return B200OPT_EINVAL;
+    if(!h->device_scale)
+        return fail(h, B200OPT_ESTATE,
+                    "b200opt_device_scale_enable has not been called");
+    // no wait and no CUDA call: the pinned page as the last finished kernel left it
+    const volatile HostResult *hr = h->host;
+    if(hr->status) {
+        h->failed = true;
+        return fail(h, B200OPT_ETIMEOUT, "a step gave up waiting for a peer rank");
+    }
+    const uint32_t bits = hr->scale_bits;
+    if(step)
+        *step = hr->epoch;
+    if(scale) {
+        if(bits)
+            memcpy(scale, &bits, 4);
+        else
+            *scale = h->device_scale_initial;  // no step has finished yet
+    }
     return B200OPT_OK;
 }
 

@@ -75,7 +75,8 @@ struct HostResult {
     uint32_t epoch;
     uint32_t where;   // 1 = wait for gradients, 2 = wait for completion
     uint32_t peer;    // rank that did not arrive
-    uint32_t pad;
+    uint32_t scale_bits;  // device-resident loss scale after this step's policy
+                          // update (bit pattern; 0 when the scale lives on the host)
     // phase timers of the last launch, nanoseconds of %globaltimer (only with
     // B200OPT_OPT_PHASE_TIMERS): wait for the peers' announcements in CTA 0,
     // kernel entry until the last CTA finished its share, the completion
@@ -792,6 +793,7 @@ __device__ __forceinline__ void step_finish(const StepParams &p, uint32_t fl,
             p.host->inf = sums[1];
             p.host->nan = sums[2];
             p.host->status = status;
+            p.host->scale_bits = p.device_scale ? __float_as_uint(my->scale) : 0u;
             p.host->epoch = p.epoch;
             if(p.timing) {
                 const unsigned long long t_end = globaltimer_ns();

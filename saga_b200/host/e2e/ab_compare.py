@@ -2,6 +2,13 @@
 the library with the b200opt optimizer op, same program, alternating runs.
 
     python saga_b200/host/e2e/ab_compare.py --gpus N [--repeats 3] [--model cifar18|resnet-50]
+                                            [--variants ref,b200,b200+buckets4,b200+dscale]
+
+Variants: "ref" the unmodified library, "b200" the integrated one; "+buckets<k>" issues the
+optimizer step as k buckets between the backward ops (B200OPT_BUCKETS), "+dscale" keeps the loss
+scale on the device (B200OPT_DEVICE_SCALE: no stream synchronise per step), "+noloss" makes the
+program read the per-batch loss never (E2E_LOSS_EVERY=0, CIFAR program only; reading a tensor
+waits for the stream, which hides what "+dscale" removes).
 
 Every run is a child process under a time limit (a run that exceeds it is reported as
 "timeout" and the comparison goes on); the integrated build's runs also report the device
@@ -41,35 +48,47 @@ def main():
     ap.add_argument("--model", default="cifar18", choices=["cifar18", "resnet-50"])
     ap.add_argument("--limit", type=int, default=150, help="seconds per run")
     ap.add_argument("--batches", type=int, default=60)
-    ap.add_argument("--only", default="", choices=["", "ref", "b200"],
-                    help="run one of the two builds only")
+    ap.add_argument("--variants", default="ref,b200")
     args = ap.parse_args()
-    env = dict(os.environ, SAGA_CUDA_CONTEXTS=str(args.gpus), E2E_GPUS=str(args.gpus),
-               B200OPT_TIME_OP="1")
+    base_env = dict(os.environ, SAGA_CUDA_CONTEXTS=str(args.gpus), E2E_GPUS=str(args.gpus),
+                    B200OPT_TIME_OP="1")
     if args.model == "cifar18":
         batch = 256
-        cmds = {v: [os.path.join(BUILD, "saga_cifar18_" + v), str(batch), str(args.batches), "4"]
-                for v in ("ref", "b200")}
+        cmd = lambda lib: [os.path.join(BUILD, "saga_cifar18_" + lib), str(batch),   # noqa: E731
+                           str(args.batches), "4"]
     else:
         batch = 128
-        env.update(E2E_HW="224", E2E_LABELS="1000", E2E_TRAIN_BATCHES=str(min(args.batches, 30)),
-                   E2E_EPOCHS="3")
-        cmds = {v: [os.path.join(BUILD, "saga_e2e_" + v), "-m", "resnet-50", "-h", "-c", "-b",
-                    str(batch), "-U"] for v in ("ref", "b200")}
+        base_env.update(E2E_HW="224", E2E_LABELS="1000",
+                        E2E_TRAIN_BATCHES=str(min(args.batches, 30)), E2E_EPOCHS="3")
+        cmd = lambda lib: [os.path.join(BUILD, "saga_e2e_" + lib), "-m", "resnet-50", "-h",   # noqa: E731
+                           "-c", "-b", str(batch), "-U"]
+    variants = {}
+    for name in args.variants.split(","):
+        lib, *mods = name.split("+")
+        env = dict(base_env)
+        for m in mods:
+            if m.startswith("buckets"):
+                env["B200OPT_BUCKETS"] = m[len("buckets"):]
+            elif m == "dscale":
+                env["B200OPT_DEVICE_SCALE"] = "1"
+            elif m == "noloss":
+                env["E2E_LOSS_EVERY"] = "0"
+            else:
+                raise SystemExit("unknown variant modifier " + m)
+        variants[name] = (cmd(lib), env)
     out = {"model": args.model, "gpus": args.gpus, "batch_per_gpu": batch, "repeats": args.repeats,
-           "runs": {"ref": [], "b200": []}, "op_us": []}
+           "runs": {v: [] for v in variants}, "op_us": []}
     for _ in range(args.repeats):
-        for v in ("ref", "b200"):          # alternate, so that drift hits both alike
-            if args.only and v != args.only:
-                continue
-            r, ops = run(cmds[v], env, args.limit)
+        for v, (c, env) in variants.items():   # alternate, so that drift hits all alike
+            r, ops = run(c, env, args.limit)
             out["runs"][v].append(r["img_per_s_mean"] if r else "timeout or failure")
             if v == "b200" and ops:
                 out["op_us"].append(max(o["mean_us"] for o in ops))
-    for v in ("ref", "b200"):
+    for v in variants:
         ok = [x for x in out["runs"][v] if isinstance(x, float)]
         if ok:
-            out[v + "_img_per_s"] = {"mean": statistics.mean(ok), "min": min(ok), "max": max(ok)}
+            out[v + "_img_per_s"] = {"mean": statistics.mean(ok), "median": statistics.median(ok),
+                                     "min": min(ok), "max": max(ok)}
     if out["op_us"] and "b200_img_per_s" in out:
         op_us = statistics.mean(out["op_us"])
         step_us = 1e6 * batch * args.gpus / out["b200_img_per_s"]["mean"]

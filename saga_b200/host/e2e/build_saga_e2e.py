@@ -87,17 +87,82 @@ def patch_tree(tree):
         return head + '#include "b200_create_optimizers.inc"\n\n' + t[end:]
 
     def program_cpp(t):
+        # CudaProgram::step: the stream synchronise and the host policy block become
+        # conditional on where the loss scale lives.  Scale on the host (default):
+        # synchronise, fetch the flag sums, run the reference's own policy block.
+        # Scale on the device: b200_pace() right behind the enqueue of the step's ops
+        # keeps the host ONE step ahead of the device (it waits for the previous
+        # step's end, so the batch callbacks that follow may touch the previous
+        # step's buffers), and neither the synchronise nor the policy block runs.
         pos = t.index("m_mp_scaling *= 0.5")
         start = t.rindex("if(m_mp_enabled)", 0, pos)
-        t = t[:start] + "b200_fill_aux(*this);\n\n    " + t[start:]
+        sync = "chkCuda(cudaStreamSynchronize(m_ctx->m_stream));"
+        s0 = t.rindex(sync, 0, start)
+        assert t[s0 + len(sync):start].strip() == ""
+        t = (t[:s0] + "if(!b200_step_end(*this))\n        " + sync + "\n\n    b200_fill_aux(*this);\n\n    "
+             + "if(m_mp_enabled && !m_b200_dscale)" + t[start + len("if(m_mp_enabled)"):])
+        a = "runOps(m_ops, batch, m_pc.anomaly_detect);"
+        assert t.count(a) == 1
+        t = t.replace(a, a + "\n    b200_pace(*this);", 1)
+        # buckets of the optimizer step are moved behind the backward ops they depend on
+        b = "m_ops.insert(m_ops.end(), m_opt.begin(), m_opt.end());"
+        assert t.count(b) == 1
+        t = t.replace(b, b + "\n    b200_place_buckets(m_ops);", 1)
         a = "namespace saga {"
         i = t.index(a)
-        return t[:i] + a + "\nclass CudaProgram;\nvoid b200_fill_aux(CudaProgram &p);\n" + t[i + len(a):]
+        return (t[:i] + a + "\nclass CudaProgram;\nvoid b200_fill_aux(CudaProgram &p);\n"
+                "void b200_pace(CudaProgram &p);\nbool b200_step_end(CudaProgram &p);\n"
+                "void b200_place_buckets(CudaOps &ops);\n"
+                + t[i + len(a):])
+
+    def common_hpp(t):
+        a = "float m_mp_scaling{1};"
+        assert t.count(a) == 1
+        t = t.replace(a, a + "\n    const float *m_b200_dscale{nullptr};  // loss scale in device memory, or null", 1)
+        b = "double getMPS(void) const override { return m_mp_scaling; }"
+        assert t.count(b) == 1
+        return t.replace(b, "double getMPS(void) const override;", 1)
+
+    def kernels_cu(t):
+        import re
+        # one more parameter for the two loss-gradient kernel templates
+        t, k = re.subn(r"(catclassifier_bwd\(int n, const T \*x, T \*dx, const L \*y, const L \*dy,\s*"
+                       r"float \*loss, unsigned int channels, float scale)\)\s*\{",
+                       r"\1, const float *dscale)\n{\n    if(dscale != nullptr)\n        scale = scale * *dscale;", t)
+        assert k == 1
+        t, k = re.subn(r"(deviceLossReduction\(const T \*A, const L \*B, T \*g, float scale, float \*out,\s*"
+                       r"int N)\)\s*\{",
+                       r"\1, const float *dscale)\n{\n    if(dscale != nullptr)\n        scale = scale * *dscale;", t)
+        assert k == 1
+        # the existing launchers pass null
+        t, k = re.subn(r"loss, c, scale\);", "loss, c, scale, nullptr);", t)
+        assert k == 2
+        t, k = re.subn(r"x \+ o, dy \+ o, dx \+ o, scale, loss \+ i \* 4, c\);",
+                       "x + o, dy + o, dx + o, scale, loss + i * 4, c, nullptr);", t)
+        assert k == 3
+        end = t.rindex("};  // namespace saga")
+        return t[:end] + '#include "b200_loss_scale_kernels.inc"\n\n' + t[end:]
+
+    def dnn_cpp(t):
+        import re
+        a = '#include "cuda_kernels.hpp"'
+        assert t.count(a) == 1
+        t = t.replace(a, a + '\n#include "b200_loss_scale.hpp"', 1)
+        t, k = re.subn(r"\b(catclassifier_bwd_half_i32|loss_bwd_half_float|loss_bwd_half_half|"
+                       r"loss_bwd_float_float)\(", r"b200_\1(", t)
+        assert k == 4
+        t, k = re.subn(r"scale \* p\.m_mp_scaling, p\.m_ctx->m_stream\)",
+                       "scale, p.m_mp_scaling, p.m_b200_dscale, p.m_ctx->m_stream)", t)
+        assert k == 4
+        return t
 
     rewrite(os.path.join(tree, "src/cuda/cuda_tensor.hpp"), [storage_hpp])
     rewrite(os.path.join(tree, "src/cuda/cuda_tensor.cpp"), [storage_cpp])
     rewrite(os.path.join(tree, "src/cuda/cuda_optimizer.cpp"), [optimizer_cpp])
     rewrite(os.path.join(tree, "src/cuda/cuda_program.cpp"), [program_cpp])
+    rewrite(os.path.join(tree, "src/cuda/cuda_common.hpp"), [common_hpp])
+    rewrite(os.path.join(tree, "src/cuda/cuda_kernels.cu"), [kernels_cu])
+    rewrite(os.path.join(tree, "src/cuda/cuda_dnn.cpp"), [dnn_cpp])
 
 
 def build_variant(ref, work, name, defines, extra_inc, extra_libs):
@@ -110,7 +175,7 @@ def build_variant(ref, work, name, defines, extra_inc, extra_libs):
         procs.append(subprocess.Popen(CXX + defines + inc + ["-c", os.path.join(ref, src), "-o", obj],
                                       stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     kobj = os.path.join(work, name + "_kernels.o")
-    run(NVCC + ["-I" + os.path.join(ref, "src", "cuda"), "-c", os.path.join(ref, KERNELS), "-o", kobj])
+    run(NVCC + ["-I" + os.path.join(ref, "src", "cuda")] + extra_inc + ["-c", os.path.join(ref, KERNELS), "-o", kobj])
     mobj = os.path.join(work, name + "_main.o")
     run(CXX + defines + inc + ["-c", os.path.join(HERE, "e2e_main.cpp"), "-o", mobj])
     cobj = os.path.join(work, name + "_cifar.o")

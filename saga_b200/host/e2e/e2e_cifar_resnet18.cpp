@@ -8,6 +8,8 @@
 //
 //   e2e_cifar_resnet18 <batch_per_gpu> <batches_per_epoch> <epochs>
 //   ranks = SAGA_CUDA_CONTEXTS (one host thread per GPU, as in Saga's own tests)
+//   E2E_LOSS_EVERY=<k>: the per-batch callback reads the loss of every k-th batch
+//   only (0: never; default 1) -- reading a tensor waits for the program's stream
 //
 // Linked once against the unmodified reference library and once against the
 // library with the b200opt optimizer op; prints one JSON line.
@@ -33,6 +35,7 @@ int main(int argc, char **argv)
     const long batches = argc > 2 ? atol(argv[2]) : 40;
     const int epochs = argc > 3 ? atoi(argv[3]) : 3;
     const auto dt = Tensor::DataType::HALF;
+    const long loss_every = getenv("E2E_LOSS_EVERY") ? atol(getenv("E2E_LOSS_EVERY")) : 1;
 
     Graph g;
     auto x = makeTensor(Tensor::DataType::U8, Dims({DimParam::BATCH_SIZE, 3, 32, 32}), "input");
@@ -82,7 +85,9 @@ int main(int argc, char **argv)
                 for(int i = 0; i < batch_size; i++)
                     labels.set({i}, (int)(((uint32_t)(batch * batch_size + i + r) * 2654435761u) >> 28) % 10);
             };
-            auto post_ops = [&](long, const Program &, auto tas) {
+            auto post_ops = [&](long batch, const Program &, auto tas) {
+                if(loss_every == 0 || batch % loss_every)
+                    return;
                 auto &loss = *tas[LOSS];
                 for(int i = 0; i < batch_size; i++)
                     loss_sum += loss.get({i});

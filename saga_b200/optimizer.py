@@ -244,6 +244,12 @@ class AdamGroup:
                for r in rows]
         return np.float32(scale.value), log
 
+    def device_scale_peek(self):
+        """(scale, step) as the last finished step kernel left them; does not wait."""
+        scale, step = C.c_float(), C.c_uint32()
+        check(lib().b200opt_device_scale_peek(self._h, C.byref(scale), C.byref(step)), self._h)
+        return np.float32(scale.value), int(step.value)
+
     def step_host(self, grads_half_ptr, grads_float_ptr, lr, l2_lambda, scale, stream=0):
         out = (C.c_uint32 * 3)()
         check(lib().b200opt_step_host(self._h, C.c_void_p(grads_half_ptr),

@@ -51,10 +51,20 @@ def test_device_scale_matches_host_loop(oracle, policy, interval):
         g.device_scale_enable(1024.0, policy, max(interval, 1), log_capacity=64)
         stack = [dev_u16(G[0]) for G in grads]
         torch.cuda.synchronize()
+        # before any step: the initial scale, step 0
+        assert g.device_scale_peek() == (np.float32(1024.0), 0)
+        seen = []
         for step in range(steps):        # no host synchronise inside this loop
             gr.view(torch.int16).copy_(stack[step], non_blocking=True)
             g.exec_device_scale(1e-3, 0.01, stream_ptr())
+            seen.append(g.device_scale_peek())   # does not wait: any finished step's value
         scale, log = g.device_scale_read(stream_ptr(), capacity=64)
+        # every peek saw the scale that belongs to the step number it came with
+        # (or the initial one), and after the wait it is the last step's
+        for s, k in seen:
+            assert 0 <= k <= steps
+        peek_scale, peek_step = g.device_scale_peek()
+        assert peek_step == steps and peek_scale.tobytes() == scales[-1].tobytes()
         assert len(log) == steps
         for k in range(steps):
             assert log[k][:3] == flags[k], (k, log[k], flags[k])

@@ -20,13 +20,28 @@ BUILD = os.path.join(ROOT, "saga_b200", "host", "e2e", "_build")
 REF, B200 = os.path.join(BUILD, "saga_parity_ref"), os.path.join(BUILD, "saga_parity_b200")
 
 
-def _run(exe, *args):
-    env = dict(os.environ, SAGA_CUDA_CONTEXTS="1", CUDA_VISIBLE_DEVICES="0")
+def _run(exe, *args, gpus=1, **extra_env):
+    env = dict(os.environ, SAGA_CUDA_CONTEXTS=str(gpus),
+               CUDA_VISIBLE_DEVICES=",".join(map(str, range(gpus))))
+    env.update({k: str(v) for k, v in extra_env.items()})
     res = subprocess.run([exe, *map(str, args)], capture_output=True, text=True, timeout=600, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     lines = [ln for ln in res.stdout.splitlines() if ln.startswith('{"parity"')]
     assert lines, res.stdout[-2000:]
-    return json.loads(lines[-1])
+    out = json.loads(lines[-1])
+    # what the integrated build reports about itself on stderr (one JSON object per line)
+    for ln in res.stderr.splitlines():
+        if ln.startswith('{"b200_'):
+            for key, val in json.loads(ln).items():
+                if val.get("rank", 0) == 0:
+                    out[key] = val
+    return out
+
+
+def _same_tensors(dir_a, dir_b, names):
+    for name in names:
+        a, b = opt.tensor_load(dir_a / name), opt.tensor_load(dir_b / name)
+        assert a.shape == b.shape and a.tobytes() == b.tobytes(), f"{name} differs"
 
 
 @pytest.mark.skipif(not (os.path.exists(REF) and os.path.exists(B200)),
@@ -61,3 +76,100 @@ def test_integrated_build_trains_like_the_unmodified_one(tmp_path):
             moved.append(name)
     # training changed the weights of every layer
     assert {"fc1-w", "fc2-w", "fc3-w"} <= set(moved), f"training changed only {moved} of {names}"
+
+
+BUILT = pytest.mark.skipif(not os.path.exists(B200),
+                           reason="end-to-end programs not built (no Saga checkout at build time)")
+
+
+@BUILT
+def test_loss_scale_on_the_device_follows_the_host_policy_build(tmp_path):
+    """The integrated build with the loss scale kept on the device (the loss-gradient
+    kernel reads it through a device pointer, the step kernel applies the policy, and
+    CudaProgram::step no longer waits for the stream) against the same build with the
+    reference's host-side policy block: 800 batches in ONE Program::run without a single
+    tensor read in between, against 800 single-batch runs with the scale read after each.
+    The run is long enough for the scale to climb into fp16 overflow and be halved.  The
+    per-step log the device keeps must equal the host trajectory bit for bit, and so must
+    every trained tensor."""
+    steps = 800
+    init, out_host, out_dev = tmp_path / "init", tmp_path / "host", tmp_path / "dev"
+    _run(B200, "init", init)
+    names = sorted(os.listdir(init))
+    host = _run(B200, "train", init, out_host, steps)
+    dev = _run(B200, "train", init, out_dev, steps, "oneshot", B200OPT_DEVICE_SCALE=1,
+               B200OPT_SCALE_LOG=1024, B200OPT_PRINT_SCALE_LOG=1, E2E_LOSS_EVERY=0)
+    log = dev["b200_scale_log"]
+    assert log["steps"] == steps and len(host["scale_bits"]) == steps
+    assert log["scale_bits"] == host["scale_bits"], "device-side scale trajectory differs"
+    assert dev["scale_bits"] == host["scale_bits"][-1:]          # Program::getMPS reads it back
+    # the policy had something to decide: overflow steps halved the scale
+    overflow = [k for k, f in enumerate(log["flags"]) if f[1] or f[2]]
+    assert overflow, "no overflow step in the run: the trajectory is a plain x1.02 ramp"
+    _same_tensors(out_host, out_dev, names)
+
+
+@BUILT
+@pytest.mark.parametrize("buckets,layout", [(3, "graph"), (2, "reference"), (16, "graph")])
+def test_buckets_behind_backward_train_like_the_whole_step(tmp_path, buckets, layout):
+    """The optimizer step issued as buckets between the backward ops (side stream, gated
+    by events) against the same build with one op behind all of backward: same scale
+    trajectory and bit-identical trained tensors, with the flat layout in backward order
+    and in the reference's order."""
+    steps = 60
+    init, out_whole, out_b = tmp_path / "init", tmp_path / "whole", tmp_path / "buckets"
+    _run(B200, "init", init)
+    names = sorted(os.listdir(init))
+    whole = _run(B200, "train", init, out_whole, steps)
+    bucketed = _run(B200, "train", init, out_b, steps, B200OPT_BUCKETS=buckets,
+                    B200OPT_LAYOUT=layout, B200OPT_PRINT_PLAN=1)
+    plan = bucketed["b200_bucket_plan"]["buckets"]
+    assert 2 <= len(plan) <= min(buckets, 6)       # six trainable tensors in this model
+    # consecutive ranges that cover the fp16 buffer; issue points never move backwards
+    at = 0
+    for b in plan:
+        assert b["half"][0] == at
+        at += b["half"][1]
+    assert [b["after_op"] for b in plan] == sorted(b["after_op"] for b in plan)
+    if layout == "graph":       # the first bucket goes out well before backward ends
+        assert plan[0]["after_op"] < bucketed["b200_bucket_plan"]["ops"] - 1
+    assert bucketed["scale_bits"] == whole["scale_bits"]
+    _same_tensors(out_whole, out_b, names)
+
+
+@BUILT
+@pytest.mark.multigpu
+def test_buckets_on_two_gpus_train_like_the_whole_step(tmp_path):
+    """Two ranks (one host thread per GPU, Saga's threading model): every bucket's kernel
+    waits for the peer's same bucket, reduces both ranks' gradients and writes the weights
+    into both ranks' buffers while the rest of backward is still running.  Same layout,
+    so the shards and with them the per-shard flags are the same: bit-identical result."""
+    steps = 40
+    init, out_whole, out_b = tmp_path / "init", tmp_path / "whole", tmp_path / "buckets"
+    _run(B200, "init", init)
+    names = sorted(os.listdir(init))
+    whole = _run(B200, "train", init, out_whole, steps, gpus=2)
+    bucketed = _run(B200, "train", init, out_b, steps, gpus=2, B200OPT_BUCKETS=3,
+                    B200OPT_LAYOUT="reference")
+    assert whole["ranks"] == bucketed["ranks"] == 2
+    assert bucketed["scale_bits"] == whole["scale_bits"]
+    _same_tensors(out_whole, out_b, names)
+    # backward order moves tensors between the two shards; results stay the same as long
+    # as no range flag is raised (the x0.9 rule counts shards), which 40 steps do not reach
+    graph = _run(B200, "train", init, tmp_path / "graph", steps, gpus=2, B200OPT_BUCKETS=3)
+    assert graph["scale_bits"] == whole["scale_bits"]
+    _same_tensors(out_whole, tmp_path / "graph", names)
+
+
+@BUILT
+@pytest.mark.multigpu
+def test_loss_scale_on_the_device_two_gpus(tmp_path):
+    steps = 300
+    init, out_host, out_dev = tmp_path / "init", tmp_path / "host", tmp_path / "dev"
+    _run(B200, "init", init)
+    names = sorted(os.listdir(init))
+    host = _run(B200, "train", init, out_host, steps, gpus=2)
+    dev = _run(B200, "train", init, out_dev, steps, "oneshot", gpus=2, B200OPT_DEVICE_SCALE=1,
+               B200OPT_SCALE_LOG=512, B200OPT_PRINT_SCALE_LOG=1, E2E_LOSS_EVERY=0)
+    assert dev["b200_scale_log"]["scale_bits"] == host["scale_bits"]
+    _same_tensors(out_host, out_dev, names)
