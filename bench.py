@@ -51,6 +51,9 @@ TENSORS = 160
 LR, L2, SCALE0 = 1e-3, 0.01, 1024.0
 NVLINK_NOMINAL_GBS = 900.0
 HBM_FALLBACK_GBS = 6650.0
+# DRAM bytes per parameter of the one-rank step kernel, from one ncu capture (--set full, two
+# launches at 2^26 parameters: 1819.9 and 1820.4 MB read + written per launch)
+NCU_DRAM_BYTES_PER_PARAM = 1820.15e6 / (1 << 26)
 METRIC = ("fused grad-reduce+Adam params/sec (gradient elements reduced and applied per second, "
           "summed over ranks: N ranks x n parameters / step time)")
 WORKLOAD = "config2: 25.6M fp16 params in 160 tensors, 1 optimizer step"
@@ -1034,11 +1037,14 @@ def main():
         achieved = alg_bytes / (per_step_ms * 1e-3) / 1e9
         roof_hbm = {
             "bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-            "frac": achieved / hbm_peak, "traffic": None,
+            "frac": achieved / hbm_peak,
+            "traffic": NCU_DRAM_BYTES_PER_PARAM * n if world == 1 and not f32 else None,
             "peak_kind": f"of {peak_kind}", "algorithmic_bytes_per_launch": alg_bytes,
             "frac_of_8000_nominal": achieved / 8000.0,
-            "traffic_note": "dram bytes of one launch come from an ncu capture, which this run "
-                            "does not make; the committed summary under profiles/ holds them",
+            "traffic_note": "not measured by this run: dram__bytes_read.sum + dram__bytes_write.sum "
+                            "of one launch of the one-rank kernel from an ncu capture at 2^26 "
+                            "parameters (1820 MB), scaled to this launch in proportion to the "
+                            "parameters (every array is passed over once); null for other kernels",
         }
         cfg = base_config(n, len(sizes), wl)
         run = {
@@ -1076,7 +1082,7 @@ def main():
         if world == 1:
             line["roofline"] = roof_hbm
         else:
-            # SURVEY's algorithmic bytes per NVLink direction: reduce-scatter + all-gather of
+            # algorithmic bytes per NVLink direction: reduce-scatter + all-gather of
             # fp16 (fp32) buffers = 4n(N-1)/N (8n(N-1)/N); what the path in use puts on the
             # links is reported beside it
             nv_alg = (8 if f32 else 4) * n * (world - 1) / world
