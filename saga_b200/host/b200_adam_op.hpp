@@ -246,9 +246,14 @@ struct B200Adam : public CudaOperation {
     {
         if(m_on_destroy)
             m_on_destroy();  // lets the owner forget the handle first
-        if(m_timed_steps)
-            fprintf(stderr, "{\"b200_adam_op\": {\"rank\": %d, \"steps\": %ld, \"mean_us\": %.2f}}\n",
-                    m_ctx->m_nccl_rank, m_timed_steps, 1e3 * m_timed_ms / m_timed_steps);
+        if(m_timed_steps) {
+            // one write per line: the rank threads end at about the same time
+            char line[160];
+            const int len = snprintf(line, sizeof(line),
+                                     "{\"b200_adam_op\": {\"rank\": %d, \"steps\": %ld, \"mean_us\": %.2f}}\n",
+                                     m_ctx->m_nccl_rank, m_timed_steps, 1e3 * m_timed_ms / m_timed_steps);
+            fwrite(line, 1, (size_t)len, stderr);
+        }
         if(m_device_scale && getenv("B200OPT_PRINT_SCALE_LOG"))
             print_scale_log();
         for(cudaEvent_t e : {m_ev[0], m_ev[1], m_step_ev[0], m_step_ev[1], m_fork, m_join})

@@ -18,6 +18,7 @@ step and its fraction of the bytes-moved roofline follow.  Prints one JSON line.
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 
@@ -36,9 +37,21 @@ def run(cmd, env, limit):
     if res.returncode != 0:
         return None, None
     line = [ln for ln in res.stdout.splitlines() if ln.startswith('{"e2e"')]
-    ops = [json.loads(ln)["b200_adam_op"] for ln in res.stderr.splitlines()
-           if ln.startswith('{"b200_adam_op"')]
-    return (json.loads(line[-1]) if line else None), ops
+    ops = []
+    for ln in res.stderr.splitlines():       # one object per rank thread
+        if ln.startswith('{"b200_adam_op"'):
+            try:
+                ops.append(json.loads(ln)["b200_adam_op"])
+            except ValueError:
+                pass                         # two ranks' lines ran into each other
+    if not line:
+        return None, ops
+    # printf spells a non-finite mean loss "nan" / "inf", which is not JSON
+    text = re.sub(r"-?\bnan\b", "NaN", re.sub(r"\binf\b", "Infinity", line[-1]))
+    try:
+        return json.loads(text), ops
+    except ValueError:
+        return None, ops
 
 
 def main():
@@ -82,6 +95,9 @@ def main():
         for v, (c, env) in variants.items():   # alternate, so that drift hits all alike
             r, ops = run(c, env, args.limit)
             out["runs"][v].append(r["img_per_s_mean"] if r else "timeout or failure")
+            if r and "loss_mean_rank0" in r:   # the CIFAR program reports these
+                out.setdefault("loss_mean", {}).setdefault(v, []).append(r["loss_mean_rank0"])
+                out.setdefault("loss_scale", {}).setdefault(v, []).append(r["loss_scale_rank0"])
             if v == "b200" and ops:
                 out["op_us"].append(max(o["mean_us"] for o in ops))
     for v in variants:
