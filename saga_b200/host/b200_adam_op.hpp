@@ -352,6 +352,11 @@ struct B200Adam : public CudaOperation {
     void enable_buckets(const std::vector<B200BucketRange> &ranges)
     {
         m_buckets = ranges;
+        // B200OPT_BUCKET_GRID=<ctas>: the buckets that run beside backward take this many
+        // CTAs instead of a grid that fills the GPU, and so leave room for backward's own
+        // kernels; the last bucket, behind which nothing else runs, keeps the full grid
+        if(const char *e = getenv("B200OPT_BUCKET_GRID"))
+            m_bucket_grid = std::max(0L, atol(e));
         cudaStreamCreateWithFlags(&m_side, cudaStreamNonBlocking);
         cudaEventCreateWithFlags(&m_fork, cudaEventDisableTiming);
         cudaEventCreateWithFlags(&m_join, cudaEventDisableTiming);
@@ -367,6 +372,8 @@ struct B200Adam : public CudaOperation {
             cudaEventRecord(m_fork, p.m_ctx->m_stream);
             cudaStreamWaitEvent(m_side, m_fork, 0);
             const auto &r = m_buckets[i];
+            if(m_bucket_grid)
+                b200opt_set_option(m_handle, B200OPT_OPT_GRID, last ? 0 : m_bucket_grid);
             rc = b200opt_step_bucket(m_handle, r.half_first, r.half_count, r.float_first,
                                      r.float_count, p.m_pc.learning_rate, p.m_pc.l2_lambda,
                                      p.m_mp_scaling, m_side, last ? 1 : 0);
@@ -458,6 +465,7 @@ struct B200Adam : public CudaOperation {
     cudaEvent_t m_step_ev[2] = {nullptr, nullptr};
     long m_steps = 0;
     std::vector<B200BucketRange> m_buckets;
+    long m_bucket_grid = 0;
     cudaStream_t m_side = nullptr;
     cudaEvent_t m_fork = nullptr, m_join = nullptr;
     std::function<void()> m_on_destroy;

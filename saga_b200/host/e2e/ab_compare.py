@@ -6,7 +6,9 @@ the library with the b200opt optimizer op, same program, alternating runs.
 
 Variants: "ref" the unmodified library, "b200" the integrated one; "+buckets<k>" issues the
 optimizer step as k buckets between the backward ops (B200OPT_BUCKETS), "+dscale" keeps the loss
-scale on the device (B200OPT_DEVICE_SCALE: no stream synchronise per step), "+noloss" makes the
+scale on the device (B200OPT_DEVICE_SCALE: no stream synchronise per step), "+grid<c>" gives the
+buckets that run beside backward c CTAs (B200OPT_BUCKET_GRID), "+layoutref" keeps the reference's
+tensor order in the flat buffer (B200OPT_LAYOUT=reference), "+noloss" makes the
 program read the per-batch loss never (E2E_LOSS_EVERY=0, CIFAR program only; reading a tensor
 waits for the stream, which hides what "+dscale" removes).
 
@@ -82,6 +84,10 @@ def main():
         for m in mods:
             if m.startswith("buckets"):
                 env["B200OPT_BUCKETS"] = m[len("buckets"):]
+            elif m.startswith("grid"):
+                env["B200OPT_BUCKET_GRID"] = m[len("grid"):]
+            elif m == "layoutref":
+                env["B200OPT_LAYOUT"] = "reference"
             elif m == "dscale":
                 env["B200OPT_DEVICE_SCALE"] = "1"
             elif m == "noloss":

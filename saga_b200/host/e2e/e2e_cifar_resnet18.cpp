@@ -52,6 +52,13 @@ int main(int argc, char **argv)
     n = g.addNode("avgpool", n->y(), {{"global", true}});
     n = g.addNode("fc", n->y(), {{"outputs", 10}, {"bias", true}}, "fc");
     n = g.addNode("catclassifier", n->y());
+    // The node declares its per-sample loss output as ONE float (src/node.cpp:336-337 of
+    // the Saga tree) while the backward kernel writes one float per sample
+    // (src/cuda/cuda_kernels.cu:35-65): with a batch of 256 that runs a kilobyte past the
+    // allocation into whichever managed block follows it.  Declared per batch here, so
+    // that both library builds run this program without that overflow.
+    n->m_outputs["loss"] =
+        makeTensor(Tensor::DataType::FLOAT, Dims({DimParam::BATCH_SIZE, 1}), "loss");
 
     const auto LABELS = n->m_outputs["y"]->grad();
     const auto LOSS = n->m_outputs["loss"];

@@ -29,7 +29,10 @@ def test_anchored_edits_apply_to_the_checkout(tmp_path):
     for f in ("cuda_tensor.hpp", "cuda_tensor.cpp", "cuda_optimizer.cpp", "cuda_program.cpp",
               "cuda_common.hpp", "cuda_kernels.cu", "cuda_dnn.cpp"):
         shutil.copy(os.path.join(REF, "src", "cuda", f), tree / "src" / "cuda" / f)
+    shutil.copy(os.path.join(REF, "src", "node.cpp"), tree / "src" / "node.cpp")
     mod.patch_tree(str(tree))
+    node = (tree / "src" / "node.cpp").read_text()
+    assert 'Dims({x->m_dims[0], 1}), "loss")' in node and 'Dims({1, 1}), "loss")' not in node
     opt = (tree / "src" / "cuda" / "cuda_optimizer.cpp").read_text()
     assert '#include "b200_create_optimizers.inc"' in opt
     assert "CudaProgram::create_optimizers()" not in opt          # the original is gone
