@@ -223,6 +223,36 @@ b200_plan_buckets(const std::vector<B200PlanEntry> &entries, int nbuckets, bool 
     return plan;
 }
 
+// Moves the bucket ops of a program's op list behind the ops they depend on.
+//   is_bucket(op)  true for the ops to move (they sit at the end of the list, in
+//                  bucket order, when this is called)
+//   anchor_of(op)  the op a bucket has to follow
+//   is_final(op)   true for the op that closes the step: a bucket whose anchor is
+//                  not in the list goes right in front of it
+// Everything else keeps its order; buckets keep theirs, also when several share an
+// anchor.  Generic over the op type so that it can be checked without Saga's headers.
+template <typename Op, typename IsBucket, typename AnchorOf, typename IsFinal>
+void
+b200_place_behind_anchors(std::vector<Op> &ops, IsBucket is_bucket, AnchorOf anchor_of,
+                          IsFinal is_final)
+{
+    std::vector<Op> buckets, rest;
+    for(auto &op : ops)
+        (is_bucket(op) ? buckets : rest).push_back(op);
+    ops = rest;
+    for(auto &b : buckets) {
+        auto at = std::find(ops.begin(), ops.end(), anchor_of(b));
+        if(at == ops.end()) {
+            at = std::find_if(ops.begin(), ops.end(), is_final);
+        } else {
+            ++at;
+            while(at != ops.end() && is_bucket(*at))
+                ++at;
+        }
+        ops.insert(at, b);
+    }
+}
+
 #ifdef HAVE_B200OPT  // the part below needs Saga's own headers
 
 // Non-owning view of library memory, so that tensor storages can alias it the

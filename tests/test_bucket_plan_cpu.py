@@ -9,6 +9,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 PROGRAM = r'''
 #include <cstdio>
 #include <cstdlib>
+#include <string>
 #include <vector>
 #include "b200_adam_op.hpp"
 
@@ -107,6 +108,21 @@ int main()
         if(well_formed(f, p))
             return 1;
         CHECK(p.buckets.size() == 2 && p.buckets[1].half_count == padded(90000));
+    }
+    {
+        // placement in the op list: ops are strings, buckets are "B<k>@<anchor>", "END" closes
+        // the step; they arrive at the end of the list in bucket order
+        std::vector<std::string> ops = {"f0", "f1", "b1", "b0", "B0@b1", "B1@b1", "B2@b0", "B3@gone", "END"};
+        auto is_bucket = [](const std::string &s) { return s[0] == 'B'; };
+        auto anchor_of = [](const std::string &s) { return s.substr(s.find('@') + 1); };
+        auto is_final = [](const std::string &s) { return s == "END"; };
+        b200_place_behind_anchors(ops, is_bucket, anchor_of, is_final);
+        CHECK(ops == (std::vector<std::string>{"f0", "f1", "b1", "B0@b1", "B1@b1", "b0", "B2@b0",
+                                               "B3@gone", "END"}));
+        // nothing to move: unchanged
+        std::vector<std::string> plain = {"f0", "b0", "END"};
+        b200_place_behind_anchors(plain, is_bucket, anchor_of, is_final);
+        CHECK(plain == (std::vector<std::string>{"f0", "b0", "END"}));
     }
     // random programs: always well formed
     srand(7);
