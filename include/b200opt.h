@@ -277,6 +277,11 @@ B200OPT_API int b200opt_step_bucket(b200opt_t *h, size_t half_first,
  * and grads_float (n_float fp32) into the gradient buffers on `stream`, steps,
  * waits for the stream and returns the flag sums.  Either pointer may be NULL
  * when its group is empty.  Pinned host memory makes the copies asynchronous.
+ * On one rank, from 2^22 fp16 elements up, the copy is cut into eight chunks
+ * on a stream of the library's own and the step is issued as one bucket per
+ * chunk behind it (b200opt_step_bucket), so that the update overlaps the
+ * transfer; the result is bit for bit that of one whole step.  The first such
+ * call creates that stream and its events.
  */
 B200OPT_API int b200opt_step_host(b200opt_t *h, const void *grads_half,
                       const void *grads_float, float lr, float l2_lambda,

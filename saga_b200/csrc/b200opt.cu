@@ -90,6 +90,11 @@ struct b200opt {
     bool step_open = false;      // between b200opt_step_begin and the last bucket
     uint32_t *scale_log = nullptr;
     uint32_t scale_log_cap = 0;
+    // b200opt_step_host on one rank: the gradient copy runs on a stream of its own,
+    // chunk by chunk, while the step consumes the chunks that have arrived
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t copy_fork = nullptr;
+    cudaEvent_t copy_done[16] = {};
     std::string err;
 };
 
@@ -537,6 +542,13 @@ int b200opt_destroy(b200opt_t *h)
         cudaFree(h->arena);
     cudaFree(h->state);
     cudaFree(h->scale_log);
+    if(h->copy_stream) {
+        cudaStreamDestroy(h->copy_stream);
+        cudaEventDestroy(h->copy_fork);
+        for(cudaEvent_t e : h->copy_done)
+            if(e)
+                cudaEventDestroy(e);
+    }
     if(h->host)
         cudaFreeHost(h->host);
     cudaGetLastError();
@@ -1230,6 +1242,49 @@ int b200opt_step_host(b200opt_t *h, const void *grads_half,
         return B200OPT_EINVAL;
     DeviceGuard guard(h->device);
     cudaStream_t st = (cudaStream_t)stream;
+    // One rank, a buffer worth splitting: the copy is cut into chunks on a copy
+    // stream and the step is issued as one bucket per chunk behind it, so that the
+    // update of a chunk overlaps the transfer of the next ones.  Buckets of one
+    // step give bit for bit the result of one whole step.
+    constexpr size_t kPipelineMin = (size_t)1 << 22;  // fp16 elements
+    constexpr int kChunks = 8;
+    if(h->nranks == 1 && !h->serial && h->n_half >= kPipelineMin && !h->step_open &&
+       !h->failed) {
+        if(!h->copy_stream) {
+            CK(h, cudaStreamCreateWithFlags(&h->copy_stream, cudaStreamNonBlocking));
+            CK(h, cudaEventCreateWithFlags(&h->copy_fork, cudaEventDisableTiming));
+            for(int c = 0; c < kChunks; c++)
+                CK(h, cudaEventCreateWithFlags(&h->copy_done[c], cudaEventDisableTiming));
+        }
+        // the copy may not overtake what the caller's stream still does with the buffers
+        CK(h, cudaEventRecord(h->copy_fork, st));
+        CK(h, cudaStreamWaitEvent(h->copy_stream, h->copy_fork, 0));
+        int rc = b200opt_step_begin(h);
+        if(rc)
+            return rc;
+        const size_t per = (h->n_half / kChunks + 4095) & ~(size_t)4095;
+        size_t first = 0;
+        for(int c = 0; c < kChunks && rc == B200OPT_OK; c++) {
+            const bool last = c == kChunks - 1;
+            const size_t count = last ? h->n_half - first : std::min(per, h->n_half - first);
+            if(c == 0 && h->n_float)
+                CK(h, cudaMemcpyAsync(h->arena + h->off_gf, grads_float, h->n_float * 4,
+                                      cudaMemcpyHostToDevice, h->copy_stream));
+            if(count)
+                CK(h, cudaMemcpyAsync(h->arena + h->off_gh + first * 2,
+                                      (const char *)grads_half + first * 2, count * 2,
+                                      cudaMemcpyHostToDevice, h->copy_stream));
+            CK(h, cudaEventRecord(h->copy_done[c], h->copy_stream));
+            CK(h, cudaStreamWaitEvent(st, h->copy_done[c], 0));
+            // the fp32 group travels with the first chunk
+            rc = b200opt_step_bucket(h, first, count, 0, c == 0 ? h->n_float : 0, lr, l2_lambda,
+                                     scale, stream, last ? 1 : 0);
+            first += count;
+        }
+        if(rc)
+            return rc;
+        return b200opt_flags(h, stream, flags_out);
+    }
     if(h->n_half)
         CK(h, cudaMemcpyAsync(h->arena + h->off_gh, grads_half, h->n_half * 2,
                               cudaMemcpyHostToDevice, st));

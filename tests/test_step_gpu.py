@@ -302,6 +302,59 @@ def test_step_host_takes_host_gradients(oracle):
         g.destroy()
 
 
+def test_step_host_pipelines_large_buffers_bit_for_bit(oracle):
+    """Above 2^22 fp16 elements b200opt_step_host cuts the gradient copy into chunks on a
+    copy stream and issues the step as one bucket per chunk behind it.  Same gradients
+    through that call and through a plain device step: flags, m, v, master (both groups)
+    and fp16 weights must come out bit for bit the same, also when the same host buffer
+    is refilled and sent again right away."""
+    n_half, n_float = (1 << 22) + 4112, 528
+    W0, Wf0 = synth.weights_half(n_half, seed=16), synth.weights_float(n_float, seed=16)
+    groups = [AdamGroup.create(0, 1, 0, n_half, n_float) for _ in range(2)]
+    try:
+        for g in groups:
+            w, _ = g.buffers(capi.HALF)
+            wf, _ = g.buffers(capi.FLOAT)
+            w.view(torch.int16).copy_(dev_u16(W0))
+            wf.copy_(dev_f32(Wf0))
+            g.init_master(stream_ptr())
+        a, b = groups
+        _, ga = a.buffers(capi.HALF)
+        _, gaf = a.buffers(capi.FLOAT)
+        hg = torch.empty(n_half, dtype=torch.int16).pin_memory()
+        hf = torch.empty(n_float, dtype=torch.float32).pin_memory()
+        scale = np.float32(64.0)
+        for step in range(1, 5):
+            G = synth.grads_half(n_half, scale, step, seed=16)
+            Gf = synth.grads_float(n_float, scale, step, seed=16)
+            if step == 2:
+                G[n_half - 77] = 0x7C00          # +inf in the last chunk
+                G[5] = 0x7800                    # 32768 in the first
+            if step == 3:
+                G[n_half // 2 + 1] = 0x7E00      # NaN in the middle
+            hg.copy_(torch.from_numpy(G.view(np.int16)))
+            hf.copy_(torch.from_numpy(Gf))
+            ga.view(torch.int16).copy_(hg, non_blocking=True)
+            gaf.copy_(hf, non_blocking=True)
+            a.exec(1e-3, 0.01, scale, stream_ptr())
+            fa = a.flags(stream_ptr())
+            fb = b.step_host(hg.data_ptr(), hf.data_ptr(), 1e-3, 0.01, scale, stream_ptr())
+            assert fa == fb == {2: (1, 1, 0), 3: (1, 0, 1)}.get(step, (0, 0, 0))
+            scale = oracle.policy_reference(scale, fa)
+        assert a.iter == b.iter == 4
+        for dtype in (capi.HALF, capi.FLOAT):
+            for which in range(3 if dtype == capi.HALF else 2):
+                x, y = a.export_state(dtype, which), b.export_state(dtype, which)
+                assert x.tobytes() == y.tobytes(), (dtype, which)
+            wa, _ = a.buffers(dtype)
+            wb, _ = b.buffers(dtype)
+            assert torch.equal(wa.view(torch.int16 if dtype == capi.HALF else torch.int32),
+                               wb.view(torch.int16 if dtype == capi.HALF else torch.int32))
+    finally:
+        for g in groups:
+            g.destroy()
+
+
 def test_export_import_state_resumes_exactly(oracle):
     n = 4112
     W0 = synth.weights_half(n, seed=8)
